@@ -1,6 +1,6 @@
 """The device memory the cache manager's page numbers refer to.
 
-One tensor per group, ``[entries, 2 (K and V), pages, page_size, kv_heads, head_dim]`` in the run's
+One tensor per group, ``[entries, planes (K and V, or one plane of latents), pages, page_size, kv_heads, head_dim]`` in the run's
 dtype (the reference keeps one such tensor for all layers, src/infer/kv/paged_cache.py:25-34), and
 one tensor per stateful run-order entry, ``[slots, *shape]``. A ``sink`` page may be appended to each
 group, and a sink slot to the state tensors: padded rows of a captured decode graph write there, and the
@@ -25,19 +25,23 @@ class CachePools:
         self.num_pages = list(num_pages)
         extra = 1 if sink_page else 0
         self.sink = [n if sink_page else -1 for n in num_pages]       # page index of the sink per group
-        self.kv = [torch.zeros((len(g.entries), 2, n + extra, page_size, g.need.kv_heads, g.need.head_dim),
+        self.kv = [torch.zeros((len(g.entries), g.need.planes, n + extra, page_size, g.need.kv_heads, g.need.head_dim),
                                dtype=dtype, device=device)
                    for g, n in zip(layout.groups, num_pages)]
         self.state_sink = num_state_slots if sink_page else -1        # index of the sink state slot
         self.state = {pos: torch.zeros((max(num_state_slots, 1) + extra, *need.shape), dtype=_STATE_DTYPES[need.dtype],
                                        device=device)
                       for pos, need in layout.entry_state.items()}
+        self.block_state = {pos: torch.zeros((max(num_state_slots, 1) + extra, *need.shape),
+                                             dtype=_STATE_DTYPES[need.dtype], device=device)
+                            for pos, need in layout.block_state.items()}
         self._cache_of = run_order_cache_of or []
 
     @property
     def nbytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.kv) + \
-            sum(t.numel() * t.element_size() for t in self.state.values())
+            sum(t.numel() * t.element_size() for t in self.state.values()) + \
+            sum(t.numel() * t.element_size() for t in self.block_state.values())
 
     def layer_caches(self, n_entries: int) -> list[LayerCache]:
         """One LayerCache per run-order entry."""
@@ -46,12 +50,14 @@ class CachePools:
             lc = LayerCache()
             if pos in self.layout.entry_group:
                 g, idx = self.layout.entry_group[pos]
-                lc.k, lc.v, lc.group = self.kv[g][idx, 0], self.kv[g][idx, 1], g
+                lc.k, lc.group = self.kv[g][idx, 0], g
+                lc.v = self.kv[g][idx, 1] if self.kv[g].shape[1] > 1 else None
                 lc.writes = not (pos < len(self._cache_of) and self._cache_of[pos] is not None)
             lc.state = self.state.get(pos)
+            lc.block_state = self.block_state.get(pos)
             out.append(lc)
         return out
 
     def zero_state(self, slot: int) -> None:
-        for t in self.state.values():
+        for t in list(self.state.values()) + list(self.block_state.values()):
             t[slot].zero_()

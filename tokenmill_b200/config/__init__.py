@@ -1,5 +1,6 @@
 from .engine_config import EngineConfig, add_engine_args, engine_config_from_args
-from .model_config import ConfigError, Qwen2Config, read_config_json
+from .kutirax_config import KutiraxConfig
+from .model_config import ConfigError, Qwen2Config, architecture_name, read_config_json
 
 __all__ = ["EngineConfig", "add_engine_args", "engine_config_from_args", "ConfigError", "Qwen2Config",
-           "read_config_json"]
+           "KutiraxConfig", "architecture_name", "read_config_json"]

@@ -24,6 +24,18 @@ class ConfigError(ValueError):
     """config.json is missing a key, or names an option the engine does not implement."""
 
 
+def architecture_name(raw: dict[str, Any]) -> str:
+    """The architecture a config.json names: the first of ``architectures``, or the string ``architecture``."""
+    names = raw.get("architectures") or []
+    if isinstance(names, str):
+        names = [names]
+    if not names and isinstance(raw.get("architecture"), str):
+        names = [raw["architecture"]]
+    if not names:
+        raise ConfigError("config.json names no architecture (key 'architectures' or 'architecture')")
+    return names[0]
+
+
 _REQUIRED = ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads")
 
 

@@ -1,0 +1,201 @@
+// Pieces of feed-forward layers beyond SwiGLU: the squared-relu activation, the router of a mixture of experts, the
+// gated activation of all experts at once with the routing weight folded in, and a batched 32-bit matrix product.
+//
+// tm_moe_route, one warp per token, all in 32-bit: logits[e] = x . W_r[e] + b[e]; the `top` largest logits are
+// chosen (lowest index first among equals); their weights are the softmax over the chosen logits alone. Outputs: the
+// chosen experts and weights ([T, top]) and a dense row of weights ([T, E], zero where not chosen). Each logit is
+// summed lane-wise over k = lane, lane + 32, ... and then across lanes, so it does not depend on the batch.
+//
+// tm_glu_routed: gu [T, E, 2, F] (per expert: gate rows, then up rows) -> act [T, E, F] = silu(gate) * up * weight[t, e],
+// exactly zero for experts the token did not choose (their products are never looked at), so that ONE matrix product
+// of act with the experts' down matrices laid side by side along K gives the weighted sum of the chosen experts.
+#include "common.cuh"
+
+namespace tmk {
+
+template <typename T>
+__global__ void __launch_bounds__(256) relu2_kernel(const T* __restrict__ in, T* __restrict__ out, long long total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const float v = fmaxf(to_float(in[i]), 0.f);
+    out[i] = from_float<T>(v * v);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w,
+                                                        const float* __restrict__ bias, int* __restrict__ top_idx,
+                                                        float* __restrict__ top_w, float* __restrict__ dense_w, int T_,
+                                                        int H, int E, int top) {
+  extern __shared__ float sm[];               // per warp: E logits
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= T_) return;
+  float* logit = sm + warp * E;
+  const T* row = x + (size_t)t * H;
+  for (int e = 0; e < E; ++e) {
+    float acc = 0.f;
+    for (int k = lane; k < H; k += 32) acc = fmaf(to_float(row[k]), w[(size_t)e * H + k], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) logit[e] = acc + (bias ? bias[e] : 0.f);
+  }
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) dense_w[(size_t)t * E + e] = 0.f;
+  __syncwarp();
+  // `top` rounds of arg-max; a chosen logit is marked by -inf in the scratch copy and its value kept by lane 0.
+  float best0 = 0.f, denom = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = logit[e];
+      if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (k == 0) best0 = bv;
+    const float ex = expf(bv - best0);
+    denom += ex;
+    if (lane == 0) {
+      top_idx[(size_t)t * top + k] = bi;
+      top_w[(size_t)t * top + k] = ex;
+      logit[bi] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  if (lane == 0) {
+    for (int k = 0; k < top; ++k) {
+      const float wv = top_w[(size_t)t * top + k] / denom;
+      top_w[(size_t)t * top + k] = wv;
+      dense_w[(size_t)t * E + top_idx[(size_t)t * top + k]] = wv;
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) glu_routed_kernel(const T* __restrict__ gu, const float* __restrict__ dense_w,
+                                                         T* __restrict__ act, int E, int F) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, e = blockIdx.y;
+  const float wv = dense_w[(size_t)t * E + e];
+  const T* g = gu + ((size_t)t * E + e) * 2 * F;
+  T* o = act + ((size_t)t * E + e) * F;
+  for (int i = threadIdx.x; i < F; i += blockDim.x) {
+    float v = 0.f;
+    if (wv != 0.f) {
+      const float gv = to_float(g[i]);
+      v = gv / (1.0f + expf(-gv)) * to_float(g[F + i]) * wv;
+    }
+    o[i] = from_float<T>(v);
+  }
+}
+
+// C[b][M, N] = A[b][M, K] . W[b][N, K]^T, 32-bit, every output element one accumulator walking k in order.
+constexpr int GB = 32, GK = 16;
+__global__ void __launch_bounds__(256) gemm_f32_nt_batched_kernel(const float* __restrict__ A, long long a_batch, int lda,
+                                                                  const float* __restrict__ W, long long w_batch,
+                                                                  float* __restrict__ C, long long c_batch, int ldc, int M,
+                                                                  int N, int K) {
+  __shared__ float As[GK][GB + 1];
+  __shared__ float Ws[GK][GB + 1];
+  A += (size_t)blockIdx.z * a_batch;
+  W += (size_t)blockIdx.z * w_batch;
+  C += (size_t)blockIdx.z * c_batch;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.y * GB, n0 = blockIdx.x * GB;
+  float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+  const int lc = tid & 15, lr = tid >> 4;
+  for (int k0 = 0; k0 < K; k0 += GK) {
+    const int k = k0 + lc;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = lr + 16 * i;
+      As[lc][r] = (m0 + r < M && k < K) ? A[(size_t)(m0 + r) * lda + k] : 0.f;
+      Ws[lc][r] = (n0 + r < N && k < K) ? W[(size_t)(n0 + r) * K + k] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < GK; ++kk) {
+      const float a0 = As[kk][ty * 2], a1 = As[kk][ty * 2 + 1], w0 = Ws[kk][tx * 2], w1 = Ws[kk][tx * 2 + 1];
+      acc[0][0] = fmaf(a0, w0, acc[0][0]);
+      acc[0][1] = fmaf(a0, w1, acc[0][1]);
+      acc[1][0] = fmaf(a1, w0, acc[1][0]);
+      acc[1][1] = fmaf(a1, w1, acc[1][1]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int m = m0 + ty * 2 + i, n = n0 + tx * 2 + j;
+      if (m < M && n < N) C[(size_t)m * ldc + n] = acc[i][j];
+    }
+}
+
+}  // namespace tmk
+
+extern "C" int tm_relu2(int dtype, const void* in, void* out, long long total, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == TM_DTYPE_F32)
+    return tmk::launch_pdl(tmk::relu2_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)in,
+                           (float*)out, total);
+  if (dtype == TM_DTYPE_BF16)
+    return tmk::launch_pdl(tmk::relu2_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream,
+                           (const __nv_bfloat16*)in, (__nv_bfloat16*)out, total);
+  return TM_ERR_BAD_DTYPE;
+}
+
+// x [T, H] dtype; w [E, H], bias [E] float (bias may be null); top_idx [T, top] int; top_w [T, top], dense_w [T, E] float.
+extern "C" int tm_moe_route(int dtype, const void* x, const float* w, const float* bias, int* top_idx, float* top_w,
+                            float* dense_w, int T, int H, int E, int top, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (top < 1 || top > E || E > 2048) return TM_ERR_UNSUPPORTED_SHAPE;
+  const int warps = 4;
+  const size_t smem = (size_t)warps * E * sizeof(float);
+  const dim3 grid((T + warps - 1) / warps);
+  if (dtype == TM_DTYPE_F32)
+    return tmk::launch_pdl(tmk::moe_route_kernel<float>, grid, dim3(warps * 32), smem, stream, (const float*)x, w, bias,
+                           top_idx, top_w, dense_w, T, H, E, top);
+  if (dtype == TM_DTYPE_BF16)
+    return tmk::launch_pdl(tmk::moe_route_kernel<__nv_bfloat16>, grid, dim3(warps * 32), smem, stream,
+                           (const __nv_bfloat16*)x, w, bias, top_idx, top_w, dense_w, T, H, E, top);
+  return TM_ERR_BAD_DTYPE;
+}
+
+// gu [T, E, 2, F], act [T, E, F] dtype; dense_w [T, E] float.
+extern "C" int tm_glu_routed(int dtype, const void* gu, const float* dense_w, void* act, int T, int E, int F,
+                             cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E > 65535) return TM_ERR_UNSUPPORTED_SHAPE;
+  const dim3 grid(T, E);
+  if (dtype == TM_DTYPE_F32)
+    return tmk::launch_pdl(tmk::glu_routed_kernel<float>, grid, dim3(128), 0, stream, (const float*)gu, dense_w,
+                           (float*)act, E, F);
+  if (dtype == TM_DTYPE_BF16)
+    return tmk::launch_pdl(tmk::glu_routed_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)gu,
+                           dense_w, (__nv_bfloat16*)act, E, F);
+  return TM_ERR_BAD_DTYPE;
+}
+
+// A: batch b at A + b * a_batch, rows lda apart; W: [N, K] per batch, w_batch apart; C likewise with ldc.
+extern "C" int tm_gemm_f32_nt_batched(const float* A, long long a_batch, int lda, const float* W, long long w_batch,
+                                      float* C, long long c_batch, int ldc, int batches, int M, int N, int K,
+                                      cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || batches <= 0) return 0;
+  if (K <= 0 || batches > 65535) return TM_ERR_UNSUPPORTED_SHAPE;
+  const dim3 grid((N + tmk::GB - 1) / tmk::GB, (M + tmk::GB - 1) / tmk::GB, batches);
+  if (grid.y > 65535) return TM_ERR_UNSUPPORTED_SHAPE;
+  tmk::gemm_f32_nt_batched_kernel<<<grid, 256, 0, stream>>>(A, a_batch, lda, W, w_batch, C, c_batch, ldc, M, N, K);
+  return tmk::launch_status();
+}

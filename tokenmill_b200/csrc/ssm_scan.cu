@@ -1,0 +1,218 @@
+// A selective state-space mixer's two recurrent pieces: the short causal convolution with its carried inputs,
+// and the state recurrence itself. Both read the mixer's fused input projection
+//   proj[t] = [z (inner) | x (inner) | B (groups * N) | C (groups * N) | dt (heads)]
+// and a per-request state slot [conv inputs ((taps - 1) * channels) | S (heads * vdim * N)] of 32-bit floats.
+//
+// tm_conv_silu_state: channels = inner + 2 * groups * N run a causal convolution over the request's tokens
+// (weights [channels, taps], the LAST tap weighs the current token; what lies before the step's first token comes
+// from the slot, zeros for a new request), plus bias, then silu; 32-bit arithmetic, one rounding to the activation
+// dtype. Thread (token, channel). Only the thread of a request's first row touches the slot: it computes the up to
+// taps - 1 outputs that need carried inputs, then writes the step's last taps - 1 inputs back.
+//
+// tm_ssm_scan: per head h (group g = h / (heads / groups)) and token t, all in 32-bit:
+//   dt = softplus(dt_raw + dt_bias[h])        a = exp(-exp(A_log[h]) * dt)
+//   S <- a * S + dt * B_t x_t^T               y_t = S^T C_t + D[h] * x_t
+// One block per (head, request, slice of vdim); each of a block's columns p is served by 8 lanes that hold N / 8
+// state values each in registers for the whole step. Tokens are taken in chunks of 16 through shared memory and
+// walked strictly in order, so the result does not depend on how a request was cut into steps.
+#include "common.cuh"
+
+namespace tmk {
+
+constexpr int kMaxTaps = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(256) conv_silu_state_kernel(
+    const T* __restrict__ proj, long long proj_stride, int col0, int channels, int taps,
+    const float* __restrict__ weight, const float* __restrict__ bias, float* __restrict__ state,
+    long long state_stride, const int* __restrict__ cu_q, const int* __restrict__ seq_of_token,
+    const int* __restrict__ state_slots, T* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  const int s = seq_of_token[t];
+  const int first = cu_q[s];
+  const int j = t - first;
+  const int carried = taps - 1;
+  if (j > 0 && j < carried) return;          // the first row's thread computes these
+  float w[kMaxTaps];
+  for (int k = 0; k < taps; ++k) w[k] = weight[(size_t)c * taps + k];
+  const float bv = bias ? bias[c] : 0.f;
+  const T* in = proj + col0 + c;
+  if (j >= carried) {
+    float acc = 0.f;
+    for (int k = 0; k < taps; ++k) acc = fmaf(w[k], to_float(in[(size_t)(t - carried + k) * proj_stride]), acc);
+    acc += bv;
+    out[(size_t)t * channels + c] = from_float<T>(acc / (1.0f + expf(-acc)));
+    return;
+  }
+  // j == 0: this thread owns the request's carried inputs of channel c.
+  const int q_len = cu_q[s + 1] - first;
+  float* slot = state + (size_t)state_slots[s] * state_stride + c;       // carried input i at slot[i * channels]
+  float old[kMaxTaps];
+  for (int i = 0; i < carried; ++i) old[i] = slot[(size_t)i * channels];
+  const int n_head = min(carried, q_len);
+  for (int jj = 0; jj < n_head; ++jj) {
+    float acc = 0.f;
+    for (int k = 0; k < taps; ++k) {
+      const int src = jj - carried + k;        // offset inside the step; negative: carried input carried + src
+      const float v = src >= 0 ? to_float(in[(size_t)(first + src) * proj_stride]) : old[carried + src];
+      acc = fmaf(w[k], v, acc);
+    }
+    acc += bv;
+    out[(size_t)(first + jj) * channels + c] = from_float<T>(acc / (1.0f + expf(-acc)));
+  }
+  for (int i = 0; i < carried; ++i) {
+    const int src = q_len - carried + i;
+    slot[(size_t)i * channels] = src >= 0 ? to_float(in[(size_t)(first + src) * proj_stride]) : old[i + q_len];
+  }
+}
+
+constexpr int kScanLanes = 8;        // lanes that share one column of the state
+constexpr int kScanChunk = 16;       // tokens staged at a time
+
+__device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
+
+template <typename T, int NPL>       // NPL = ceil(N / 8) state values per lane
+__global__ void __launch_bounds__(512) ssm_scan_kernel(
+    const T* __restrict__ xbc, int channels, const T* __restrict__ proj, long long proj_stride, int dt_col,
+    const float* __restrict__ A_log, const float* __restrict__ dt_bias, const float* __restrict__ Dskip,
+    float* __restrict__ state, long long state_stride, long long state_off, const int* __restrict__ cu_q,
+    const int* __restrict__ state_slots, float* __restrict__ y, int heads, int vdim, int N, int groups, int cols) {
+  extern __shared__ __align__(16) float sm[];
+  float* Bs = sm;                               // [chunk][N]
+  float* Cs = Bs + kScanChunk * N;              // [chunk][N]
+  float* xs = Cs + kScanChunk * N;              // [chunk][cols]
+  float* dts = xs + kScanChunk * cols;          // [chunk]
+  float* decs = dts + kScanChunk;               // [chunk]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int h = blockIdx.x, s = blockIdx.y, p0 = blockIdx.z * cols;
+  const int g = h / (heads / groups);
+  const int inner = heads * vdim;
+  const int tid = threadIdx.x;
+  const int r = tid & (kScanLanes - 1), pl = tid / kScanLanes;
+  const int p = p0 + pl;
+  const bool live = pl < cols && p < vdim;
+  const int first = cu_q[s], q_len = cu_q[s + 1] - first;
+  float* S = state + (size_t)state_slots[s] * state_stride + state_off + ((size_t)h * vdim + p) * N;
+  float st[NPL];
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) {
+    const int n = r + kScanLanes * i;
+    st[i] = (live && n < N) ? S[n] : 0.f;
+  }
+  const float neg_a = -expf(A_log[h]), bias = dt_bias[h], dskip = Dskip[h];
+  for (int c0 = 0; c0 < q_len; c0 += kScanChunk) {
+    const int nt = min(kScanChunk, q_len - c0);
+    __syncthreads();
+    for (int idx = tid; idx < nt * N; idx += blockDim.x) {
+      const int tt = idx / N, n = idx - tt * N;
+      const T* row = xbc + (size_t)(first + c0 + tt) * channels + inner + g * N + n;
+      Bs[idx] = to_float(row[0]);
+      Cs[idx] = to_float(row[groups * N]);
+    }
+    for (int idx = tid; idx < nt * cols; idx += blockDim.x) {
+      const int tt = idx / cols, pp = idx - tt * cols;
+      xs[idx] = p0 + pp < vdim ? to_float(xbc[(size_t)(first + c0 + tt) * channels + h * vdim + p0 + pp]) : 0.f;
+    }
+    if (tid < nt) {
+      const float dt = softplus_f(to_float(proj[(size_t)(first + c0 + tid) * proj_stride + dt_col + h]) + bias);
+      dts[tid] = dt;
+      decs[tid] = expf(neg_a * dt);
+    }
+    __syncthreads();
+    {                                            // (every lane of a warp runs the loop: the shuffles want them all)
+      for (int tt = 0; tt < nt; ++tt) {
+        const float dec = decs[tt], xv = pl < cols ? xs[tt * cols + pl] : 0.f;
+        const float dx = dts[tt] * xv;
+        const float* Bt = Bs + tt * N;
+        const float* Ct = Cs + tt * N;
+        float part = 0.f;
+#pragma unroll
+        for (int i = 0; i < NPL; ++i) {
+          const int n = r + kScanLanes * i;
+          if (n < N) {
+            st[i] = fmaf(dec, st[i], dx * Bt[n]);
+            part = fmaf(st[i], Ct[n], part);
+          }
+        }
+        part += __shfl_xor_sync(0xffffffffu, part, 1);
+        part += __shfl_xor_sync(0xffffffffu, part, 2);
+        part += __shfl_xor_sync(0xffffffffu, part, 4);
+        if (r == 0 && live) y[(size_t)(first + c0 + tt) * inner + h * vdim + p] = fmaf(dskip, xv, part);
+      }
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int n = r + kScanLanes * i;
+      if (n < N) S[n] = st[i];
+    }
+  }
+}
+
+template <typename T>
+int launch_ssm_scan(const void* xbc, int channels, const void* proj, long long proj_stride, int dt_col,
+                    const float* A_log, const float* dt_bias, const float* Dskip, float* state, long long state_stride,
+                    long long state_off, const int* cu_q, const int* state_slots, float* y, int n_seqs, int heads,
+                    int vdim, int N, int groups, cudaStream_t stream) {
+  if (N > 32 * kScanLanes || heads % groups) return TM_ERR_UNSUPPORTED_SHAPE;
+  const int cols = vdim < 64 ? vdim : 64;
+  const int threads = ((cols * kScanLanes + 31) / 32) * 32;
+  const dim3 grid(heads, n_seqs, (vdim + cols - 1) / cols);
+  const size_t smem = (size_t)(kScanChunk * (2 * N + cols + 2)) * sizeof(float);
+  const int npl = (N + kScanLanes - 1) / kScanLanes;
+#define TM_SCAN_CASE(NPL)                                                                                            \
+  if (npl <= NPL)                                                                                                    \
+    return launch_pdl(ssm_scan_kernel<T, NPL>, grid, dim3(threads), smem, stream, (const T*)xbc, channels,           \
+                      (const T*)proj, proj_stride, dt_col, A_log, dt_bias, Dskip, state, state_stride, state_off, cu_q, \
+                      state_slots, y, heads, vdim, N, groups, cols);
+  TM_SCAN_CASE(1) TM_SCAN_CASE(2) TM_SCAN_CASE(4) TM_SCAN_CASE(8) TM_SCAN_CASE(16) TM_SCAN_CASE(32)
+#undef TM_SCAN_CASE
+  return TM_ERR_UNSUPPORTED_SHAPE;
+}
+
+}  // namespace tmk
+
+// proj [T, proj_stride] dtype, channels col0 .. col0 + channels - 1 are convolved; weight [channels, taps], bias
+// [channels] float; state [slots, state_stride] float, carried inputs first; out [T, channels] dtype.
+extern "C" int tm_conv_silu_state(int dtype, const void* proj, long long proj_stride, int col0, int channels, int taps,
+                                  const float* weight, const float* bias, float* state, long long state_stride,
+                                  const int* cu_q, const int* seq_of_token, const int* state_slots, void* out, int T,
+                                  cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (taps < 1 || taps > tmk::kMaxTaps) return TM_ERR_UNSUPPORTED_SHAPE;
+  const dim3 grid(T, (channels + 255) / 256);
+  if (dtype == TM_DTYPE_F32)
+    return tmk::launch_pdl(tmk::conv_silu_state_kernel<float>, grid, dim3(256), 0, stream, (const float*)proj,
+                           proj_stride, col0, channels, taps, weight, bias, state, state_stride, cu_q, seq_of_token,
+                           state_slots, (float*)out);
+  if (dtype == TM_DTYPE_BF16)
+    return tmk::launch_pdl(tmk::conv_silu_state_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream,
+                           (const __nv_bfloat16*)proj, proj_stride, col0, channels, taps, weight, bias, state,
+                           state_stride, cu_q, seq_of_token, state_slots, (__nv_bfloat16*)out);
+  return TM_ERR_BAD_DTYPE;
+}
+
+// xbc [T, channels] dtype = [x (heads * vdim) | B (groups * N) | C (groups * N)] after convolution and silu; dt_raw is
+// column dt_col + h of proj; A_log, dt_bias, Dskip [heads] float; S of a request at state_off inside its slot,
+// laid out [heads, vdim, N]; y [T, heads * vdim] float.
+extern "C" int tm_ssm_scan(int dtype, const void* xbc, int channels, const void* proj, long long proj_stride, int dt_col,
+                           const float* A_log, const float* dt_bias, const float* Dskip, float* state,
+                           long long state_stride, long long state_off, const int* cu_q, const int* state_slots,
+                           float* y, int n_seqs, int heads, int vdim, int N, int groups, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (dtype == TM_DTYPE_F32)
+    return tmk::launch_ssm_scan<float>(xbc, channels, proj, proj_stride, dt_col, A_log, dt_bias, Dskip, state,
+                                       state_stride, state_off, cu_q, state_slots, y, n_seqs, heads, vdim, N, groups,
+                                       stream);
+  if (dtype == TM_DTYPE_BF16)
+    return tmk::launch_ssm_scan<__nv_bfloat16>(xbc, channels, proj, proj_stride, dt_col, A_log, dt_bias, Dskip, state,
+                                               state_stride, state_off, cu_q, state_slots, y, n_seqs, heads, vdim, N,
+                                               groups, stream);
+  return TM_ERR_BAD_DTYPE;
+}

@@ -108,7 +108,7 @@ class LLMEngine:
         if num_pages < 2:
             raise RuntimeError("cache budget too small for the paged pool")
         n_groups = len(layout.groups)
-        n_state = cfg.max_num_seqs if layout.entry_state else 0
+        n_state = cfg.max_num_seqs if layout.has_state else 0
         self.cache = CacheManager([num_pages] * n_groups, cfg.block_size, layout.windows, cfg.watermark,
                                   cfg.enable_prefix_caching, num_state_slots=n_state)
         self.pools = CachePools(layout, [num_pages] * n_groups, cfg.block_size, self.dtype, self.device,

@@ -93,7 +93,7 @@ class ModelRunner:
                 os.environ.get("TOKENMILL_LM_HEAD", "1") != "0":
             self._packed_output = fused.pack_rows(model.output_weight)
         if self.graph_max_batch:
-            if any(s < 0 for s in pools.sink) or (pools.state and pools.state_sink < 0):
+            if any(s < 0 for s in pools.sink) or ((pools.state or pools.block_state) and pools.state_sink < 0):
                 raise RuntimeError("decode graphs need pools built with a sink page (and a sink state slot)")
 
     # --- the step -------------------------------------------------------------------------------

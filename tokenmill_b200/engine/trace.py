@@ -22,11 +22,11 @@ from pathlib import Path
 import torch
 
 PAGE_SIZE = 16           # tokens per cache page unless --page-size says otherwise
-LIVE_REQUESTS = 4        # requests that may be live at a time (state slots are kept for twice as many)
+LIVE_REQUESTS = 4        # requests that may be live at a time: that many state slots, used again as requests end
 
 
 def run(model_dir: str, dtype_name: str, out_dir: str, max_tokens: int, stdin=None, stdout=None,
-        device: str = "cuda:0", page_size: int = PAGE_SIZE, state_slots: int = 2 * LIVE_REQUESTS) -> int:
+        device: str = "cuda:0", page_size: int = PAGE_SIZE, state_slots: int = LIVE_REQUESTS) -> int:
     from ..cache.manager import CacheManager
     from ..cache.pool import CachePools
     from ..kernels import ops
@@ -42,7 +42,8 @@ def run(model_dir: str, dtype_name: str, out_dir: str, max_tokens: int, stdin=No
         raise RuntimeError("trace_run drives the engine's CUDA kernels; no CUDA device is visible")
     dtype = resolve_dtype(dtype_name)
     dev = torch.device(device)
-    model = load_model(model_dir, dtype, dev)
+    # No request can hold more than max_tokens tokens: position tables need not reach further.
+    model = load_model(model_dir, dtype, dev, max_positions=max(int(max_tokens), 1))
     layout = model.cache_layout()
     # The pool holds exactly the pages max_tokens needs (live requests each rounded up to 64 tokens,
     # a multiple of the page size), so pages freed by one request are reused by the next.
@@ -50,7 +51,7 @@ def run(model_dir: str, dtype_name: str, out_dir: str, max_tokens: int, stdin=No
         raise ValueError(f"--page-size must divide 64 (requests are counted in units of 64 tokens), got {page_size}")
     num_pages = max(1, -(-max_tokens // page_size))
     n_groups = len(layout.groups)
-    n_state = state_slots if layout.entry_state else 0
+    n_state = state_slots if layout.has_state else 0
     cache = CacheManager([num_pages] * n_groups, page_size, layout.windows, watermark=0.0,
                          enable_prefix_caching=False, num_state_slots=n_state)
     pools = CachePools(layout, [num_pages] * n_groups, page_size, dtype, dev, num_state_slots=n_state,
@@ -106,7 +107,7 @@ def main(argv: list[str] | None = None) -> int:
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--device", default="cuda:0")
     ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per cache page (a divisor of 64)")
-    ap.add_argument("--state-slots", type=int, default=2 * LIVE_REQUESTS,
+    ap.add_argument("--state-slots", type=int, default=LIVE_REQUESTS,
                     help="slots for fixed-size per-request state, for models whose mixers keep some")
     args = ap.parse_args(argv)
     return run(args.model, args.dtype, args.out, args.max_tokens, device=args.device, page_size=args.page_size,

@@ -67,6 +67,18 @@ _SIGNATURES: dict[str, list] = {
     "tm_stream_linear_slices": [_I],
     "tm_swiglu_partials": [_P, _I, _LL, _P, _I, _I, _P],
     "tm_gemm_f32_nt": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
+    "tm_add_norm_pair": [_I, _P, _P, _P, _F, _P, _P, _P, _P, _P, _F, _P, _I, _P, _I, _I, _P],
+    "tm_token_shift": [_I, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _P],
+    "tm_gated_group_norm": [_I, _P, _P, _LL, _P, _F, _P, _I, _I, _I, _P],
+    "tm_latent_prepare": [_I, _P, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _I, _P, _P, _P, _I, _P, _P],
+    "tm_latent_attention": [_I, _P, _LL, _LL, _P, _LL, _LL, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _P, _LL, _LL,
+                            _I, _I, _I, _I, _F, _I, _P],
+    "tm_conv_silu_state": [_I, _P, _LL, _I, _I, _I, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _P],
+    "tm_ssm_scan": [_I, _P, _I, _P, _LL, _I, _P, _P, _P, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "tm_relu2": [_I, _P, _P, _LL, _P],
+    "tm_moe_route": [_I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "tm_glu_routed": [_I, _P, _P, _P, _I, _I, _I, _P],
+    "tm_gemm_f32_nt_batched": [_P, _LL, _I, _P, _LL, _P, _LL, _I, _I, _I, _I, _I, _P],
     "tm_argmax": [_P, _I, _I, _LL, _P, _P, _P, _P],
     "tm_sample": [_P, _I, _I, _LL, _P, _P, _P, _P, _P, _P, _I, _P, _P],
 }

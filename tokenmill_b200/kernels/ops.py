@@ -786,3 +786,179 @@ def tc_qkv_rope_write(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | Non
              _req(sin, "sin", torch.float32), _opt(slot_map, "slot_map", torch.int32), _req(q_out, "q_out", bf),
              _opt(kcache, "kcache", bf), _opt(vcache, "vcache", bf), T, K, nh, nkv, D, cos.shape[0],
              _tc_flag(x.device).data_ptr(), _stream())
+
+
+# --- 32-bit norms for parallel blocks, token shift ------------------------------------------------------------
+
+def add_norm_pair(resid: torch.Tensor, w1: torch.Tensor, eps: float, out1: torch.Tensor, *, dtype: torch.dtype,
+                  w2: torch.Tensor | None = None, out2: torch.Tensor | None = None, a: torch.Tensor | None = None,
+                  b: torch.Tensor | None = None, scale: float = 1.0, ids: torch.Tensor | None = None,
+                  table: torch.Tensor | None = None, rows: torch.Tensor | None = None) -> None:
+    """resid [T, H] float32 += scale * (a + b) (or = table[ids]); out1 = norm(resid) * w1 (float32 or ``dtype``),
+    out2 = norm(resid) * w2 (``dtype``, optional). 32-bit arithmetic, each output rounded once. With ``rows`` only
+    those rows are normed and the stream is not written."""
+    H = resid.shape[-1]
+    n_rows = rows.numel() if rows is not None else resid.shape[0]
+    if out1.shape[0] < n_rows or out1.shape[-1] != H or w1.numel() != H or (out2 is None) != (w2 is None):
+        raise lib.KernelError("add_norm_pair: outputs and weights do not fit the stream")
+    if out1.dtype not in (torch.float32, dtype) or (ids is None) != (table is None):
+        raise lib.KernelError("add_norm_pair: out1 is float32 or the activation dtype; ids and table come together")
+    lib.call("tm_add_norm_pair", _code(dtype), _req(resid, "resid", torch.float32), _opt(a, "a", dtype),
+             _opt(b, "b", dtype), float(scale), _opt(ids, "ids", torch.int32), _opt(table, "table", dtype),
+             _opt(rows, "rows", torch.int32), _req(w1, "w1", torch.float32), _opt(w2, "w2", torch.float32), float(eps),
+             _req(out1, "out1"), int(out1.dtype == torch.float32 and dtype != torch.float32), _opt(out2, "out2", dtype),
+             n_rows, H, _stream())
+
+
+def token_shift(h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor, seq_of_token: torch.Tensor,
+                state_slots: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = h[t] + (h[t-1] - h[t]) * mu; a request's first row takes h[t-1] from its slot of ``state``
+    [slots, >= H] float32, which then receives the request's last h of this step."""
+    T, H = h.shape
+    if state.dim() != 2 or state.shape[1] < H or mu.numel() != H or out.shape != h.shape:
+        raise lib.KernelError("token_shift: shapes do not fit")
+    lib.call("tm_token_shift", _code(out.dtype), _req(h, "h", torch.float32), _req(mu, "mu", torch.float32),
+             _req(state, "state", torch.float32), state.stride(0), _req(cu_q, "cu_q", torch.int32),
+             _req(seq_of_token, "seq_of_token", torch.int32), _req(state_slots, "state_slots", torch.int32),
+             _req(out, "out"), T, H, _stream())
+    return out
+
+
+def gated_group_norm(y: torch.Tensor, proj: torch.Tensor, weight: torch.Tensor, eps: float, groups: int,
+                     out: torch.Tensor) -> torch.Tensor:
+    """out = group_rms_norm(y * silu(z)) * weight; y [T, inner] float32, z = proj[:, :inner]."""
+    T, inner = y.shape
+    if proj.shape[0] != T or proj.shape[1] < inner or weight.numel() != inner or out.shape != y.shape:
+        raise lib.KernelError("gated_group_norm: shapes do not fit")
+    lib.call("tm_gated_group_norm", _code(out.dtype), _req(y, "y", torch.float32), _req(proj, "proj", out.dtype),
+             proj.stride(0), _req(weight, "weight", torch.float32), float(eps), _req(out, "out"), T, inner, int(groups),
+             _stream())
+    return out
+
+
+# --- attention over a cache of latents ------------------------------------------------------------------------
+
+def latent_prepare(proj: torch.Tensor, q_rank: int, rank: int, rot: int, rot_dims: int, wq: torch.Tensor,
+                   wkv: torch.Tensor, eps: float, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                   slot_map: torch.Tensor, cq_out: torch.Tensor, cache: torch.Tensor) -> None:
+    """proj [T, q_rank + rank + rot] -> cq_out [T, q_rank] (normed), cache rows slot_map[t] = [norm(c) | rope(k_rot)]."""
+    T = proj.shape[0]
+    if proj.shape[1] != q_rank + rank + rot or cache.shape[-1] != rank + rot or cos.shape[1] * 2 != rot_dims or \
+            cq_out.shape != (T, q_rank):
+        raise lib.KernelError("latent_prepare: shapes do not fit")
+    dt = proj.dtype
+    lib.call("tm_latent_prepare", _code(dt), _req(proj, "proj"), q_rank, rank, rot, rot_dims, _req(wq, "wq", torch.float32),
+             _req(wkv, "wkv", torch.float32), float(eps), _req(positions, "positions", torch.int32),
+             _req(cos, "cos", torch.float32), _req(sin, "sin", torch.float32), cos.shape[0],
+             _req(slot_map, "slot_map", torch.int32), _req(cq_out, "cq_out", dt), _req(cache, "cache", dt), T,
+             _tc_flag(proj.device).data_ptr(), _stream())
+
+
+def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, rot_dims: int,
+                     cache: torch.Tensor, block_table: torch.Tensor, cu_q: torch.Tensor, kv_before: torch.Tensor,
+                     tile_seq: torch.Tensor, tile_row0: torch.Tensor, n_tiles: int, out: torch.Tensor, *, scale: float,
+                     window: int) -> torch.Tensor:
+    """q_lat [T, nh, rank] float32, q_rot [T, nh, rot] (unrotated), out [T, nh, rank]: any strides with a unit last
+    one; cache [pages, page, 1, rank + rot]."""
+    T, nh, rank = q_lat.shape
+    rot = q_rot.shape[2]
+    dt = cache.dtype
+    for t, name in ((q_lat, "q_lat"), (q_rot, "q_rot"), (out, "out")):
+        if not t.is_cuda or t.stride(2) != 1:
+            raise lib.KernelError(f"latent_attention: {name} must be on the GPU with a unit last stride")
+    if q_lat.dtype != torch.float32 or q_rot.dtype != dt or out.dtype != dt or out.shape != q_lat.shape or \
+            cache.shape[-1] != rank + rot or cos.shape[1] * 2 != rot_dims:
+        raise lib.KernelError("latent_attention: dtypes or shapes do not fit")
+    lib.call("tm_latent_attention", _code(dt), q_lat.data_ptr(), q_lat.stride(0), q_lat.stride(1), q_rot.data_ptr(),
+             q_rot.stride(0), q_rot.stride(1), _req(cos, "cos", torch.float32), _req(sin, "sin", torch.float32), rot_dims,
+             _req(cache, "cache"), _req(block_table, "block_table", torch.int32), block_table.stride(0),
+             _req(cu_q, "cu_q", torch.int32), _req(kv_before, "kv_before", torch.int32),
+             _req(tile_seq, "tile_seq", torch.int32), _req(tile_row0, "tile_row0", torch.int32), n_tiles, out.data_ptr(),
+             out.stride(0), out.stride(1), nh, rank, rot, cache.shape[1], float(scale), int(window), _stream())
+    return out
+
+
+def bmm_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[b] = a[b] . w[b]^T for a [B, M, K], w [B, N, K] (contiguous), out [B, M, N]; a and out may be strided views
+    with a unit last stride. float32: this library's CUDA-core kernel (true 32-bit); bfloat16 in, float32 or
+    bfloat16 out: the library's batched product."""
+    B, M, K = a.shape
+    N = w.shape[1]
+    if w.shape != (B, N, K) or out.shape != (B, M, N) or a.stride(2) != 1 or out.stride(2) != 1:
+        raise lib.KernelError("bmm_nt: shapes do not fit")
+    if a.dtype == torch.float32 and w.dtype == torch.float32 and out.dtype == torch.float32:
+        lib.call("tm_gemm_f32_nt_batched", a.data_ptr(), a.stride(0), a.stride(1), _req(w, "w"), w.stride(0),
+                 out.data_ptr(), out.stride(0), out.stride(1), B, M, N, K, _stream())
+        return out
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise lib.KernelError(f"bmm_nt: unsupported operands {a.dtype} / {w.dtype}")
+    out.copy_(torch.bmm(a, w.transpose(1, 2), out_dtype=out.dtype))
+    return out
+
+
+# --- state-space mixer ----------------------------------------------------------------------------------------
+
+def conv_silu_state(proj: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: torch.Tensor | None,
+                    state: torch.Tensor, cu_q: torch.Tensor, seq_of_token: torch.Tensor, state_slots: torch.Tensor,
+                    out: torch.Tensor) -> torch.Tensor:
+    """Causal convolution + silu over columns col0 .. col0 + channels of proj [T, P]; weight [channels, taps] float32;
+    the request's last taps - 1 inputs live at the start of its slot of ``state`` [slots, n] float32."""
+    T = proj.shape[0]
+    taps = weight.shape[1]
+    if weight.shape[0] != channels or out.shape != (T, channels) or state.shape[1] < (taps - 1) * channels or \
+            col0 + channels > proj.shape[1]:
+        raise lib.KernelError("conv_silu_state: shapes do not fit")
+    lib.call("tm_conv_silu_state", _code(proj.dtype), _req(proj, "proj"), proj.stride(0), col0, channels, taps,
+             _req(weight, "weight", torch.float32), _opt(bias, "bias", torch.float32), _req(state, "state", torch.float32),
+             state.stride(0), _req(cu_q, "cu_q", torch.int32), _req(seq_of_token, "seq_of_token", torch.int32),
+             _req(state_slots, "state_slots", torch.int32), _req(out, "out", proj.dtype), T, _stream())
+    return out
+
+
+def ssm_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, A_log: torch.Tensor, dt_bias: torch.Tensor,
+             D: torch.Tensor, state: torch.Tensor, state_off: int, cu_q: torch.Tensor, state_slots: torch.Tensor,
+             y: torch.Tensor, *, n_seqs: int, heads: int, vdim: int, N: int, groups: int) -> torch.Tensor:
+    """The state recurrence over this step's tokens; y [T, heads * vdim] float32; S of a request lives at
+    ``state_off`` inside its slot, laid out [heads, vdim, N]."""
+    T, channels = xbc.shape
+    if channels != heads * vdim + 2 * groups * N or y.shape != (T, heads * vdim) or \
+            state.shape[1] < state_off + heads * vdim * N or dt_col + heads > proj.shape[1]:
+        raise lib.KernelError("ssm_scan: shapes do not fit")
+    lib.call("tm_ssm_scan", _code(xbc.dtype), _req(xbc, "xbc"), channels, _req(proj, "proj", xbc.dtype), proj.stride(0),
+             dt_col, _req(A_log, "A_log", torch.float32), _req(dt_bias, "dt_bias", torch.float32),
+             _req(D, "D", torch.float32), _req(state, "state", torch.float32), state.stride(0), int(state_off),
+             _req(cu_q, "cu_q", torch.int32), _req(state_slots, "state_slots", torch.int32), _req(y, "y", torch.float32),
+             int(n_seqs), heads, vdim, N, groups, _stream())
+    return y
+
+
+# --- feed-forwards beyond SwiGLU ------------------------------------------------------------------------------
+
+def relu2(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = max(x, 0)^2, elementwise."""
+    if out.shape != x.shape or out.dtype != x.dtype:
+        raise lib.KernelError("relu2: out must match x")
+    lib.call("tm_relu2", _code(x.dtype), _req(x, "x"), _req(out, "out"), x.numel(), _stream())
+    return out
+
+
+def moe_route(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, top: int):
+    """x [T, H]; w [E, H] float32 -> (top_idx [T, top] int32, top_w [T, top] float32, dense_w [T, E] float32)."""
+    T, H = x.shape
+    E = w.shape[0]
+    idx = torch.empty((T, top), dtype=torch.int32, device=x.device)
+    tw = torch.empty((T, top), dtype=torch.float32, device=x.device)
+    dense = torch.empty((T, E), dtype=torch.float32, device=x.device)
+    lib.call("tm_moe_route", _code(x.dtype), _req(x, "x"), _req(w, "w", torch.float32), _opt(bias, "bias", torch.float32),
+             idx.data_ptr(), tw.data_ptr(), dense.data_ptr(), T, H, E, int(top), _stream())
+    return idx, tw, dense
+
+
+def glu_routed(gu: torch.Tensor, dense_w: torch.Tensor, act: torch.Tensor, E: int, F: int) -> torch.Tensor:
+    """gu [T, E * 2 * F] (per expert gate rows then up rows) -> act [T, E * F] = silu(gate) * up * weight."""
+    T = gu.shape[0]
+    if gu.shape[1] != E * 2 * F or act.shape != (T, E * F) or dense_w.shape != (T, E):
+        raise lib.KernelError("glu_routed: shapes do not fit")
+    lib.call("tm_glu_routed", _code(gu.dtype), _req(gu, "gu"), _req(dense_w, "dense_w", torch.float32),
+             _req(act, "act", gu.dtype), T, E, F, _stream())
+    return act

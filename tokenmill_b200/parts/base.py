@@ -38,13 +38,15 @@ class LayerCache:
 
     k, v: [pages, page_size, kv_heads, head_dim] views of the entry's group pool (None for a mixer
     without paged needs). group: index of the block-table / slot-map set in StepInputs. writes:
-    False when the entry reads another entry's cache. state: [slots, *shape] per-request state."""
+    False when the entry reads another entry's cache. state: [slots, *shape] per-request state of the mixer;
+    block_state: the same for the block arrangement, where it keeps some. A cache of one plane has no v."""
 
     k: torch.Tensor | None = None
     v: torch.Tensor | None = None
     group: int = 0
     writes: bool = True
     state: torch.Tensor | None = None
+    block_state: torch.Tensor | None = None
 
 
 class PrefillUnits(NamedTuple):

@@ -25,6 +25,8 @@ class Pending:
     partials: torch.Tensor | None = None
     ids: torch.Tensor | None = None
     table: torch.Tensor | None = None
+    branch2: torch.Tensor | None = None      # a second branch output, and the multiplier of both (blocks whose
+    scale: float = 1.0                        # branches read the same stream; norms that take them: RMSNorm32)
 
     @classmethod
     def of(cls, y: torch.Tensor) -> "Pending":
@@ -36,7 +38,10 @@ class Pending:
         return cls(partials=y) if y.dim() == 3 else cls(branch=y)
 
     def kwargs(self) -> dict:
-        return {"branch": self.branch, "partials": self.partials, "ids": self.ids, "table": self.table}
+        kw = {"branch": self.branch, "partials": self.partials, "ids": self.ids, "table": self.table}
+        if self.branch2 is not None or self.scale != 1.0:
+            kw.update(branch2=self.branch2, scale=self.scale)
+        return kw
 
 
 class PreNormBlock:
@@ -66,4 +71,50 @@ class PreNormBlock:
         return {"branch": self.feed_forward.emit(b, normed)}
 
 
+class ParallelShiftBlock:
+    """``x <- x + m * (mixer(shift(norm1(x))) + feed_forward(norm2(x)))``: both branches read the same stream, the
+    sum is scaled by ``residual_mult``, and the mixer's input passes a token shift first:
+    ``h_t <- h_t + (h_{t-1} - h_t) * mu`` with the learned vector ``mu`` (tensor ``shift`` of the layer), h_{t-1}
+    the previous token's h before its own replacement, zeros before a sequence's first token. The last h of every
+    request is per-request state of the block (one row of the hidden size in 32-bit), so a prompt may be cut
+    anywhere. The feed-forward may be absent. One kernel adds the previous block's two branch outputs to the
+    stream and writes both norms; the norms are ``RMSNorm32`` parts."""
+
+    wants_run_context = True
+
+    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm, *, hidden_size: int, residual_mult: float = 1.0,
+                 token_shift: bool = True, shift_name: str = "shift", dtype: torch.dtype, device: torch.device):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+        self.hidden_size, self.mult, self.shifts, self.shift_name = hidden_size, float(residual_mult), token_shift, shift_name
+        self.dtype, self.device = dtype, device
+        self.mu: torch.Tensor | None = None
+
+    def weight_specs(self):
+        from .spec import WeightSpec
+        return [WeightSpec(self.shift_name, (self.hidden_size,), dtype="float32", init=("normal", 0.3, 0.5))] if self.shifts else []
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        if self.shifts:
+            self.mu = tensors[self.shift_name]
+
+    def state_need(self):
+        from .spec import StateNeed
+        return StateNeed((self.hidden_size,), "float32") if self.shifts else None
+
+    def forward(self, resid: torch.Tensor, pending: Pending, step: StepInputs, cache: LayerCache) -> Pending:
+        from ..kernels import ops
+        if self.feed_forward is not None:
+            h, g = self.mixer_norm.forward(resid, pair=self.feed_forward_norm, raw=self.shifts, **pending.kwargs())
+        else:
+            h, g = self.mixer_norm.forward(resid, raw=self.shifts, **pending.kwargs()), None
+        if self.shifts:
+            shifted = torch.empty(h.shape, dtype=self.dtype, device=h.device)
+            h = ops.token_shift(h, self.mu, cache.block_state, step.cu_q, step.seq_of_token, step.state_slots, shifted)
+        mixed = self.mixer.forward(h, step, cache)
+        fed = self.feed_forward.forward(g, step) if self.feed_forward is not None else None
+        return Pending(branch=mixed, branch2=fed, scale=self.mult)
+
+
 register_block("pre_norm", PreNormBlock)
+register_block("parallel_shift", ParallelShiftBlock)

@@ -33,18 +33,34 @@ class CacheGroup:
 class CacheLayout:
     groups: list[CacheGroup]
     entry_group: dict[int, tuple[int, int]]   # run-order position -> (group, index within group)
-    entry_state: dict[int, StateNeed]         # run-order position -> per-request state need
+    entry_state: dict[int, StateNeed]         # run-order position -> per-request state need of the mixer
+    block_state: dict[int, StateNeed] = None  # run-order position -> per-request state need of the block arrangement
+
+    def __post_init__(self):
+        if self.block_state is None:
+            self.block_state = {}
+
+    @property
+    def has_state(self) -> bool:
+        """Whether requests need a state slot."""
+        return bool(self.entry_state or self.block_state)
 
     def bytes_per_token(self, elt_bytes: int) -> int:
-        return sum(2 * len(g.entries) * g.need.kv_heads * g.need.head_dim * elt_bytes for g in self.groups)
+        return sum(g.need.planes * len(g.entries) * g.need.kv_heads * g.need.head_dim * elt_bytes for g in self.groups)
 
     @property
     def windows(self) -> list[int | None]:
         return [g.need.window for g in self.groups]
 
 
-def _build(role: str, spec: PartSpec, dtype: torch.dtype, device: torch.device):
+def _build(role: str, spec: PartSpec | None, dtype: torch.dtype, device: torch.device):
+    if spec is None:
+        return None
     return get_part(role, spec.kind)(dtype=dtype, device=device, **spec.params)
+
+
+def _full_name(prefix: str, name: str) -> str:
+    return f"{prefix}.{name}" if name else prefix
 
 
 class DecoderModel:
@@ -58,11 +74,17 @@ class DecoderModel:
             ffn = _build("feed_forward", layer.feed_forward, dtype, device)
             n1 = _build("norm", layer.mixer_norm, dtype, device)
             n2 = _build("norm", layer.feed_forward_norm, dtype, device)
-            self.blocks.append(get_part("block", layer.block)(mixer, ffn, n1, n2))
+            block_cls = get_part("block", layer.block)
+            context = {"dtype": dtype, "device": device} if getattr(block_cls, "wants_run_context", False) else {}
+            block = block_cls(mixer, ffn, n1, n2, **layer.block_params, **context)
+            self.blocks.append(block)
             self._named += [(f"{layer.prefix}.{layer.mixer_name}", mixer),
                             (f"{layer.prefix}.{layer.feed_forward_name}", ffn),
                             (f"{layer.prefix}.{layer.mixer_norm_name}", n1),
                             (f"{layer.prefix}.{layer.feed_forward_norm_name}", n2)]
+            if callable(getattr(block, "weight_specs", None)):       # an arrangement with tensors of its own
+                self._named.append((layer.prefix, block))
+            self._named = [(p, part) for p, part in self._named if part is not None]
         self.final_norm = _build("norm", spec.final_norm, dtype, device)
         self._named.append((spec.final_norm_prefix, self.final_norm))
         self.embedding: torch.Tensor | None = None
@@ -76,7 +98,7 @@ class DecoderModel:
         s = self.spec
         out = [WeightSpec(s.embedding_name, (s.vocab_size, s.hidden_size))]
         for prefix, part in self._named:
-            out += [WeightSpec(f"{prefix}.{w.name}", w.shape, w.dtype, w.init) for w in part.weight_specs()]
+            out += [WeightSpec(_full_name(prefix, w.name), w.shape, w.dtype, w.init) for w in part.weight_specs()]
         if s.lm_head_name is not None:
             out.append(WeightSpec(s.lm_head_name, (s.vocab_size, s.hidden_size)))
         return out
@@ -86,7 +108,7 @@ class DecoderModel:
         self.embedding = tensors[s.embedding_name]
         self.output_weight = self.embedding if s.lm_head_name is None else tensors[s.lm_head_name]
         for prefix, part in self._named:
-            part.bind({w.name: tensors[f"{prefix}.{w.name}"] for w in part.weight_specs()})
+            part.bind({w.name: tensors[_full_name(prefix, w.name)] for w in part.weight_specs()})
 
     # --- what the engine asks the parts -----------------------------------------------------------
 
@@ -94,7 +116,7 @@ class DecoderModel:
         """Every part of the model, layer by layer (mixer, feed-forward, the two norms), then the final norm."""
         out = []
         for blk in self.blocks:
-            out += [blk.mixer, blk.feed_forward, blk.mixer_norm, blk.feed_forward_norm]
+            out += [p for p in (blk.mixer, blk.feed_forward, blk.mixer_norm, blk.feed_forward_norm) if p is not None]
         return out + [self.final_norm]
 
     def max_positions(self) -> int:
@@ -113,7 +135,8 @@ class DecoderModel:
         """Working memory of a step of n_tokens: the 32-bit residual stream, a normed copy, and the largest
         layer's own need (layers run one after another and reuse the memory)."""
         H = self.spec.hidden_size
-        per_layer = max((part_activation_bytes(b.mixer, n_tokens, H) + part_activation_bytes(b.feed_forward, n_tokens, H)
+        per_layer = max((part_activation_bytes(b.mixer, n_tokens, H) +
+                         (part_activation_bytes(b.feed_forward, n_tokens, H) if b.feed_forward is not None else 0)
                          for b in self.blocks), default=0)
         return n_tokens * H * 8 + per_layer
 
@@ -124,8 +147,12 @@ class DecoderModel:
         by_key: dict[tuple, int] = {}
         entry_group: dict[int, tuple[int, int]] = {}
         entry_state: dict[int, StateNeed] = {}
+        block_state: dict[int, StateNeed] = {}
         for pos, entry in enumerate(self.spec.run_order):
             mixer = self.blocks[entry.layer].mixer
+            block_need = getattr(self.blocks[entry.layer], "state_need", None)
+            if callable(block_need) and block_need() is not None:
+                block_state[pos] = block_need()
             need = mixer.cache_need()
             if entry.cache_of is not None:
                 owner = self.blocks[self.spec.run_order[entry.cache_of].layer].mixer.cache_need()
@@ -142,7 +169,7 @@ class DecoderModel:
             st = mixer.state_need()
             if st is not None:
                 entry_state[pos] = st
-        return CacheLayout(groups, entry_group, entry_state)
+        return CacheLayout(groups, entry_group, entry_state, block_state)
 
     # --- run ------------------------------------------------------------------------------------
 
@@ -153,7 +180,8 @@ class DecoderModel:
         step parameter "logits" ([n_want, vocab] float32, which the caller allocates)."""
         from ..kernels.program import OP_GEMM_BF16, ProgramBuilder
         s = self.spec
-        parts = [p for blk in self.blocks for p in (blk, blk.mixer, blk.feed_forward, blk.mixer_norm, blk.feed_forward_norm)]
+        parts = [p for blk in self.blocks for p in (blk, blk.mixer, blk.feed_forward, blk.mixer_norm, blk.feed_forward_norm)
+                 if p is not None]
         if self.dtype != torch.bfloat16 or not all(hasattr(p, "emit") for p in parts + [self.final_norm]):
             return None
         b = ProgramBuilder(self.device, self.dtype)

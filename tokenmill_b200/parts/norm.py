@@ -51,4 +51,46 @@ class RMSNorm:
         return out
 
 
+class RMSNorm32:
+    """RMSNorm whose every product is 32-bit: ``x * rsqrt(mean(x^2) + eps) * (offset + w)``, rounded once. ``offset``
+    is 1 for checkpoints that store the weight around zero (it is added when the weight is bound). The stream may
+    receive two branch outputs with a common multiplier on the way (``resid += scale * (branch + branch2)``), and
+    one pass can serve two norms of the same stream: ``pair`` names the second norm, whose output is returned
+    beside this one's; ``raw`` keeps this norm's output in 32-bit (for a token shift that follows)."""
+
+    def __init__(self, *, hidden_size: int, eps: float, offset: float = 0.0, weight_name: str = "weight",
+                 dtype: torch.dtype, device: torch.device):
+        self.hidden_size, self.eps, self.offset = hidden_size, float(eps), float(offset)
+        self.weight_name = weight_name
+        self.dtype, self.device = dtype, device
+        self.weight: torch.Tensor | None = None
+
+    def weight_specs(self) -> list[WeightSpec]:
+        init = ("normal", 0.1) if self.offset else ("ones_plus_normal", 0.1)
+        return [WeightSpec(self.weight_name, (self.hidden_size,), dtype="float32", init=init)]
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        w = tensors[self.weight_name]
+        self.weight = (w + self.offset).contiguous() if self.offset else w
+
+    def forward(self, resid: torch.Tensor, out: torch.Tensor | None = None, *, branch: torch.Tensor | None = None,
+                branch2: torch.Tensor | None = None, scale: float = 1.0, partials: torch.Tensor | None = None,
+                ids: torch.Tensor | None = None, table: torch.Tensor | None = None, rows: torch.Tensor | None = None,
+                pair: "RMSNorm32 | None" = None, raw: bool = False):
+        if partials is not None:
+            raise NotImplementedError("the 32-bit norm takes branch outputs, not partial products")
+        n = rows.numel() if rows is not None else resid.shape[0]
+        if out is None:
+            out = torch.empty((n, self.hidden_size), dtype=torch.float32 if raw else self.dtype, device=resid.device)
+        out2 = None
+        if pair is not None:
+            if pair.eps != self.eps or pair.hidden_size != self.hidden_size:
+                raise ValueError("two norms served by one pass share eps and width")
+            out2 = torch.empty((n, self.hidden_size), dtype=self.dtype, device=resid.device)
+        ops.add_norm_pair(resid, self.weight, self.eps, out, dtype=self.dtype, w2=pair.weight if pair is not None else None,
+                          out2=out2, a=branch, b=branch2, scale=scale, ids=ids, table=table, rows=rows)
+        return (out, out2) if pair is not None else out
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("rmsnorm32", RMSNorm32)

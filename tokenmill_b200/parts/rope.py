@@ -16,12 +16,15 @@ _TABLES: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
 
 
 class RotaryEmbedding:
-    def __init__(self, *, head_dim: int, theta: float, max_positions: int):
+    def __init__(self, *, head_dim: int, theta: float, max_positions: int, precise: bool = False):
         if head_dim % 2:
             raise ValueError(f"rotary position encoding needs an even head_dim, got {head_dim}")
         self.head_dim = head_dim
         self.theta = float(theta)
         self.max_positions = int(max_positions)
+        # precise: frequencies and angles in 64-bit, rounded once to the 32-bit tables (for designs that define the
+        # angle as position * theta^(-2i/D) without naming an order of 32-bit operations)
+        self.precise = bool(precise)
 
     def limit_positions(self, n: int) -> None:
         """No position >= n will be asked for: the tables are built that short
@@ -30,7 +33,11 @@ class RotaryEmbedding:
 
     def tables(self, device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
         """(cos, sin), each [max_positions, head_dim / 2] float32 on ``device``; shared between layers."""
-        key = (self.head_dim, self.theta, self.max_positions, str(device))
+        key = (self.head_dim, self.theta, self.max_positions, str(device), self.precise)
+        if key not in _TABLES and self.precise:
+            inv_freq = self.theta ** (-torch.arange(0, self.head_dim, 2, dtype=torch.float64) / self.head_dim)
+            freqs = torch.outer(torch.arange(self.max_positions, dtype=torch.float64), inv_freq)
+            _TABLES[key] = (freqs.cos().float().to(device).contiguous(), freqs.sin().float().to(device).contiguous())
         if key not in _TABLES:
             inv_freq = 1.0 / (self.theta ** (torch.arange(0, self.head_dim, 2, dtype=torch.int64).float()
                                              / self.head_dim))

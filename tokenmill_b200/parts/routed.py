@@ -1,0 +1,96 @@
+"""Feed-forward layers beyond SwiGLU: a dense layer with a squared-relu activation, and a mixture of experts.
+
+``SquaredReluFeedForward``: ``W_down relu(W_up h)^2``, no biases.
+
+``RoutedExperts``: E small gated feed-forwards ``W_down (silu(W_gate h) * (W_up h))`` of which each token uses
+``top``. Router logits ``W_r h + b`` are 32-bit; the ``top`` largest are chosen and weighted by a softmax over the
+chosen logits alone; the output is the weighted sum of the chosen experts' outputs. The experts' gate and up
+matrices are held as one matrix [E, 2, F, H] and their down matrices side by side along K as [H, E F]: the
+activation kernel writes silu(gate) * up * weight for the chosen experts and exact zeros for the others, so the
+second product sums the chosen experts with their weights in its 32-bit accumulator.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..registry import register_feed_forward
+from .base import StepInputs
+from .spec import WeightSpec
+
+
+class SquaredReluFeedForward:
+    def __init__(self, *, hidden_size: int, intermediate_size: int, names: dict[str, str] | None = None,
+                 dtype: torch.dtype, device: torch.device):
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.dtype, self.device = dtype, device
+        self.names = {"up": "up", "down": "down", **(names or {})}
+        self.w_up = self.w_down = None
+
+    def weight_specs(self) -> list[WeightSpec]:
+        H, I = self.hidden_size, self.intermediate_size
+        return [WeightSpec(self.names["up"], (I, H), init=("normal", 0.05)),
+                WeightSpec(self.names["down"], (H, I), init=("normal", 0.05))]
+
+    def activation_bytes(self, n_tokens: int) -> int:
+        return n_tokens * (2 * self.intermediate_size + self.hidden_size) * (4 if self.dtype == torch.float32 else 2)
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.w_up, self.w_down = tensors[self.names["up"]], tensors[self.names["down"]]
+
+    def forward(self, x: torch.Tensor, step: StepInputs | None = None) -> torch.Tensor:
+        up = ops.linear(x, self.w_up)
+        ops.relu2(up, up)
+        return ops.linear(up, self.w_down)
+
+
+class RoutedExperts:
+    def __init__(self, *, hidden_size: int, expert_size: int, num_experts: int, top: int,
+                 names: dict[str, str] | None = None, dtype: torch.dtype, device: torch.device):
+        if not 1 <= top <= num_experts:
+            raise ValueError(f"top ({top}) must lie between 1 and the number of experts ({num_experts})")
+        self.hidden_size, self.F, self.E, self.top = hidden_size, expert_size, num_experts, top
+        self.dtype, self.device = dtype, device
+        # {e} is the expert's number
+        self.names = {"router": "router", "router_bias": "router.b", "gate": "e{e}.gate", "up": "e{e}.up",
+                      "down": "e{e}.down", **(names or {})}
+        self.w_router = self.b_router = self.w_gate_up = self.w_down = None
+
+    def weight_specs(self) -> list[WeightSpec]:
+        H, F, n = self.hidden_size, self.F, self.names
+        specs = []
+        for e in range(self.E):
+            specs += [WeightSpec(n["gate"].format(e=e), (F, H), init=("normal", 0.05)),
+                      WeightSpec(n["up"].format(e=e), (F, H), init=("normal", 0.05)),
+                      WeightSpec(n["down"].format(e=e), (H, F), init=("normal", 0.05))]
+        specs += [WeightSpec(n["router"], (self.E, H), dtype="float32", init=("normal", 0.3)),
+                  WeightSpec(n["router_bias"], (self.E,), dtype="float32", init=("normal", 0.3))]
+        return specs
+
+    def activation_bytes(self, n_tokens: int) -> int:
+        elt = 4 if self.dtype == torch.float32 else 2
+        return n_tokens * ((3 * self.E * self.F + self.hidden_size) * elt + 8 * self.E)
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        n = self.names
+        self.w_router, self.b_router = tensors[n["router"]], tensors[n["router_bias"]]
+        self.w_gate_up = torch.cat([t for e in range(self.E) for t in (tensors[n["gate"].format(e=e)],
+                                                                       tensors[n["up"].format(e=e)])], dim=0).contiguous()
+        self.w_down = torch.cat([tensors[n["down"].format(e=e)] for e in range(self.E)], dim=1).contiguous()
+
+    def route(self, x: torch.Tensor):
+        """(chosen experts [T, top] int32, their weights [T, top] float32, dense weights [T, E] float32)."""
+        return ops.moe_route(x, self.w_router, self.b_router, self.top)
+
+    def forward(self, x: torch.Tensor, step: StepInputs | None = None) -> torch.Tensor:
+        T = x.shape[0]
+        _idx, _w, dense = self.route(x)
+        gu = ops.linear(x, self.w_gate_up)                                   # [T, E * 2 * F]
+        act = torch.empty((T, self.E * self.F), dtype=self.dtype, device=x.device)
+        ops.glu_routed(gu, dense, act, self.E, self.F)
+        return ops.linear(act, self.w_down)
+
+
+register_feed_forward("relu2", SquaredReluFeedForward)
+register_feed_forward("routed_experts", RoutedExperts)

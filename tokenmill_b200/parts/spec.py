@@ -19,26 +19,31 @@ class WeightSpec:
            "float32" - held in 32-bit whatever the run's dtype (norm weights, biases: small vectors
                        whose arithmetic is 32-bit in the kernels);
            "int32"   - an integer table.
-    init:  how the random-weights writer fills it: ("normal", std) or ("ones_plus_normal", std).
+    init:  how the random-weights writer fills it: ("normal", std), ("normal", std, mean) or
+           ("ones_plus_normal", std).
+    An empty ``name`` stands for the part's prefix itself (a part whose one tensor has no name of its own).
     """
 
     name: str
     shape: tuple[int, ...]
     dtype: str = "compute"
-    init: tuple[str, float] = ("normal", 0.02)
+    init: tuple = ("normal", 0.02)
 
 
 @dataclass(frozen=True)
 class PagedKVNeed:
     """A mixer that keeps per-token keys and values. window=None: all keys stay; window=w: a query at
-    position p reads keys p-w+1..p only, and pages wholly behind every future window are given back."""
+    position p reads keys p-w+1..p only, and pages wholly behind every future window are given back.
+    planes=2: a key row and a value row per token; planes=1: one row per token (a cache of latents, from
+    which keys and values are both derived)."""
 
     kv_heads: int
     head_dim: int
     window: int | None = None
+    planes: int = 2
 
     def group_key(self) -> tuple:
-        return ("paged_kv", self.kv_heads, self.head_dim, self.window)
+        return ("paged_kv", self.kv_heads, self.head_dim, self.window, self.planes)
 
 
 @dataclass(frozen=True)
@@ -66,13 +71,14 @@ class LayerSpec:
     prefix: str
     block: str                      # arrangement, e.g. "pre_norm"
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: PartSpec | None   # None: the layer has no feed-forward (arrangements that allow it)
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: PartSpec | None
     mixer_name: str = "self_attn"                       # checkpoint sub-prefix of each part's tensors
     feed_forward_name: str = "mlp"
     mixer_norm_name: str = "input_layernorm"
     feed_forward_norm_name: str = "post_attention_layernorm"
+    block_params: dict = field(default_factory=dict)    # sizes and constants of the arrangement itself
 
 
 @dataclass(frozen=True)

@@ -1,0 +1,88 @@
+"""Selective state-space mixer (the Mamba-2 form: one scalar decay per head and token).
+
+From the mixer's input h: ``W_in h = [z (inner) | x (inner) | B (G N) | C (G N) | dt (heads)]`` with inner =
+heads * vdim. x, B and C pass a short causal convolution per channel (bias, silu). Per head (head h reads group
+h // (heads / G)), in 32-bit:
+    dt = softplus(dt + dt_bias)          S <- exp(-exp(A_log) dt) S + dt B x^T          y = S^T C + D x
+then y * silu(z), RMS norm in ``norm_groups`` equal parts (each by its own root mean square) times a weight, W_o.
+
+Per request the mixer keeps, in ONE state slot of 32-bit floats: the last ``taps - 1`` inputs of the convolution
+[(taps - 1), channels], then S [heads, vdim, N]. The slot is zero for a new request. Prompt portions and single
+decoded tokens run through the same two kernels; the recurrence walks a request's tokens in order whatever the cut.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..registry import register_mixer
+from .base import LayerCache, StepInputs
+from .spec import StateNeed, WeightSpec
+
+
+class StateSpaceMixer:
+    def __init__(self, *, hidden_size: int, num_heads: int, value_dim: int, state_size: int, groups: int, conv_taps: int,
+                 norm_groups: int, eps: float, names: dict[str, str] | None = None, dtype: torch.dtype,
+                 device: torch.device):
+        if num_heads % groups:
+            raise ValueError(f"heads ({num_heads}) must be a multiple of groups ({groups})")
+        self.hidden_size, self.nh, self.dv, self.N, self.G = hidden_size, num_heads, value_dim, state_size, groups
+        self.taps, self.norm_groups, self.eps = conv_taps, norm_groups, float(eps)
+        self.inner = num_heads * value_dim
+        if self.inner % norm_groups:
+            raise ValueError(f"inner size ({self.inner}) must be a multiple of norm_groups ({norm_groups})")
+        if not 1 <= conv_taps <= 16 or state_size > 256:
+            raise ValueError("convolutions of 1 to 16 taps and states of up to 256 per column are built")
+        self.channels = self.inner + 2 * groups * state_size
+        self.proj_width = 2 * self.inner + 2 * groups * state_size + num_heads
+        self.conv_len = (conv_taps - 1) * self.channels
+        self.dtype, self.device = dtype, device
+        self.names = {"in": "in", "conv": "conv", "conv_bias": "conv.b", "dt_bias": "dt_bias", "A_log": "A_log", "D": "D",
+                      "norm": "norm", "o": "o", **(names or {})}
+        self.w_in = self.w_conv = self.b_conv = self.dt_bias = self.A_log = self.D = self.g = self.w_o = None
+
+    def weight_specs(self) -> list[WeightSpec]:
+        n, H = self.names, self.hidden_size
+        f32 = dict(dtype="float32")
+        return [WeightSpec(n["in"], (self.proj_width, H), init=("normal", 0.05)),
+                WeightSpec(n["conv"], (self.channels, self.taps), init=("normal", 0.3), **f32),
+                WeightSpec(n["conv_bias"], (self.channels,), init=("normal", 0.1), **f32),
+                WeightSpec(n["dt_bias"], (self.nh,), init=("normal", 0.5), **f32),
+                WeightSpec(n["A_log"], (self.nh,), init=("normal", 0.5), **f32),
+                WeightSpec(n["D"], (self.nh,), init=("ones_plus_normal", 0.2), **f32),
+                WeightSpec(n["norm"], (self.inner,), init=("ones_plus_normal", 0.1), **f32),
+                WeightSpec(n["o"], (H, self.inner), init=("normal", 0.05))]
+
+    def cache_need(self):
+        return None
+
+    def state_need(self) -> StateNeed:
+        return StateNeed((self.conv_len + self.nh * self.dv * self.N,), "float32")
+
+    def activation_bytes(self, n_tokens: int) -> int:
+        elt = 4 if self.dtype == torch.float32 else 2
+        return n_tokens * ((self.proj_width + self.channels + self.inner + self.hidden_size) * elt + self.inner * 4)
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        n = self.names
+        self.w_in, self.w_o = tensors[n["in"]], tensors[n["o"]]
+        self.w_conv, self.b_conv = tensors[n["conv"]], tensors[n["conv_bias"]]
+        self.dt_bias, self.A_log, self.D, self.g = tensors[n["dt_bias"]], tensors[n["A_log"]], tensors[n["D"]], tensors[n["norm"]]
+
+    def forward(self, x: torch.Tensor, step: StepInputs, cache: LayerCache) -> torch.Tensor:
+        T, dev = x.shape[0], x.device
+        proj = ops.linear(x, self.w_in)                                       # [T, z | x | B | C | dt]
+        xbc = torch.empty((T, self.channels), dtype=self.dtype, device=dev)
+        ops.conv_silu_state(proj, self.inner, self.channels, self.w_conv, self.b_conv, cache.state, step.cu_q,
+                            step.seq_of_token, step.state_slots, xbc)
+        y = torch.empty((T, self.inner), dtype=torch.float32, device=dev)
+        ops.ssm_scan(xbc, proj, self.inner + self.channels, self.A_log, self.dt_bias, self.D, cache.state, self.conv_len,
+                     step.cu_q, step.state_slots, y, n_seqs=step.n_seqs, heads=self.nh, vdim=self.dv, N=self.N,
+                     groups=self.G)
+        gated = torch.empty((T, self.inner), dtype=self.dtype, device=dev)
+        ops.gated_group_norm(y, proj, self.g, self.eps, self.norm_groups, gated)
+        return ops.linear(gated, self.w_o)
+
+
+register_mixer("state_space", StateSpaceMixer)

@@ -17,7 +17,7 @@ from pathlib import Path
 
 import torch
 
-from ..config.model_config import read_config_json
+from ..config.model_config import architecture_name, read_config_json
 from ..parts.model import DecoderModel
 from ..parts.spec import ModelSpec, WeightSpec
 from ..registry import get_architecture
@@ -68,10 +68,7 @@ def _target_dtype(spec: WeightSpec, run_dtype: torch.dtype) -> torch.dtype:
 def read_spec(folder: str | Path) -> tuple[ModelSpec, object]:
     """(ModelSpec, typed config) of a model folder, through the architecture registry."""
     raw, gen = read_config_json(folder)
-    names = raw.get("architectures") or []
-    if not names:
-        raise ValueError(f"config.json in {folder} names no architecture (key 'architectures')")
-    arch = get_architecture(names[0])
+    arch = get_architecture(architecture_name(raw))
     cfg = arch.config_from_dict(raw, gen)
     return arch.build_spec(cfg), cfg
 

@@ -25,11 +25,12 @@ def random_tensors(model: DecoderModel, seed: int, store_dtype: torch.dtype) -> 
     gen = torch.Generator(device="cpu").manual_seed(int(seed))
     out: dict[str, torch.Tensor] = {}
     for spec in model.weight_specs():
-        kind, std = spec.init
+        kind, std = spec.init[0], spec.init[1]
+        mean = spec.init[2] if len(spec.init) > 2 else 0.0
         if spec.dtype == "int32":
             out[spec.name] = torch.zeros(spec.shape, dtype=torch.int32)
             continue
-        t = torch.empty(spec.shape, dtype=torch.float32).normal_(0.0, std, generator=gen)
+        t = torch.empty(spec.shape, dtype=torch.float32).normal_(0.0, std, generator=gen) + mean
         if kind == "ones_plus_normal":
             t += 1.0
         elif kind != "normal":
@@ -45,10 +46,8 @@ def write_random_model(folder: str | Path, config: dict, seed: int = 0, store_dt
 
     folder = Path(folder)
     folder.mkdir(parents=True, exist_ok=True)
-    names = config.get("architectures") or []
-    if not names:
-        raise ValueError("the configuration names no architecture (key 'architectures')")
-    arch = get_architecture(names[0])
+    from ..config.model_config import architecture_name
+    arch = get_architecture(architecture_name(config))
     cfg = arch.config_from_dict(config, None)
     spec = arch.build_spec(cfg)
     model = DecoderModel(spec, torch.float32, torch.device("cpu"))      # declarations only; nothing runs
