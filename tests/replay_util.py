@@ -121,7 +121,8 @@ def run_trace(model_dir: Path, dtype: str, steps: list[dict], max_tokens: int, o
                page_size=page_size or PAGE_SIZE) == 0
     done = [line for line in stdout.getvalue().splitlines() if line.startswith("done ")]
     assert [int(d.split()[1]) for d in done] == [s["step"] for s in steps]
-    vocab = json.loads((Path(model_dir) / "config.json").read_text())["vocab_size"]
+    raw = json.loads((Path(model_dir) / "config.json").read_text())
+    vocab = raw["vocab_size"] if "vocab_size" in raw else raw["vocab"]
     out = {}
     for s in steps:
         wanted = sum(len(e["want"]) for e in s["entries"])

@@ -92,8 +92,60 @@ NAMED_SIZES = {
 }
 
 
+def kutirax_latent(*, heads, dim, rot_dim, vdim, q_rank, kv_rank, window, scale=None, base=10000.0, rot_dims=None) -> dict:
+    """The ``mixer`` entry of a Kutirax latent-attention layer."""
+    return {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank,
+            "scale": float(scale if scale is not None else (dim + rot_dim) ** -0.5), "mask": {"size": window},
+            "rot": {"base": float(base), "dims": rot_dims if rot_dims is not None else rot_dim}}
+
+
+def kutirax_mamba(*, heads, vdim, state, groups=1, conv=4, norm_groups=1) -> dict:
+    """The ``mixer`` entry of a Kutirax state-space layer."""
+    return {"heads": heads, "vdim": vdim, "state": state, "groups": groups, "conv": conv, "norm_groups": norm_groups}
+
+
+def kutirax_config(*, vocab, width, layers, eps=1e-5, residual_mult=1.0) -> dict:
+    """config.json of a Kutirax model. ``layers``: (type, mixer entry, mlp) with mlp None, ("dense", ff) or
+    ("moe", experts, top, ff)."""
+    out = []
+    for kind, mixer, mlp in layers:
+        if mlp is None:
+            m = None
+        elif mlp[0] == "dense":
+            m = {"kind": "dense", "ff": mlp[1]}
+        else:
+            m = {"kind": "moe", "router": {"experts": mlp[1], "top": mlp[2]}, "expert": {"ff": mlp[3]}}
+        out.append({"type": kind, "mixer": mixer, "mlp": m})
+    return {"architecture": "Kutirax", "vocab": vocab, "width": width, "norm": {"eps": eps},
+            "residual_mult": residual_mult, "layers": out}
+
+
+def _kutirax_named(name: str) -> dict | None:
+    L, M = "latent_attention", "mamba2"
+    if name == "kutirax-tiny-a":     # two windows (two cache groups), partial rotation, a layer without feed-forward, top == experts
+        return kutirax_config(vocab=211, width=48, eps=1e-6, residual_mult=0.7, layers=[
+            (L, kutirax_latent(heads=3, dim=16, rot_dim=8, vdim=12, q_rank=24, kv_rank=40, window=9, scale=0.2), ("moe", 5, 2, 24)),
+            (M, kutirax_mamba(heads=6, vdim=10, state=12, groups=3, conv=3, norm_groups=3), ("dense", 64)),
+            (L, kutirax_latent(heads=2, dim=8, rot_dim=12, vdim=20, q_rank=16, kv_rank=24, window=20, rot_dims=8, base=300.0), None),
+            (M, kutirax_mamba(heads=2, vdim=24, state=16, groups=1, conv=4, norm_groups=1), ("moe", 3, 3, 16))])
+    if name == "kutirax-tiny-b":     # starts with a state-space layer, one expert per token, a window across two pages
+        lat = kutirax_latent(heads=5, dim=24, rot_dim=16, vdim=24, q_rank=32, kv_rank=48, window=33, scale=0.15, base=500000.0)
+        return kutirax_config(vocab=300, width=80, eps=1e-5, residual_mult=1.0, layers=[
+            (M, kutirax_mamba(heads=4, vdim=20, state=8, groups=4, conv=2, norm_groups=4), None),
+            (L, lat, ("dense", 100)), (L, lat, ("moe", 8, 1, 20))])
+    if name == "kutirax-tiny-c":     # sizes that are multiples of nothing: 7 heads, rank 72, 50 columns of 20 states, 5 taps
+        return kutirax_config(vocab=130, width=56, eps=1e-5, residual_mult=0.5, layers=[
+            (M, kutirax_mamba(heads=3, vdim=50, state=20, groups=1, conv=5, norm_groups=2), ("dense", 40)),
+            (L, kutirax_latent(heads=7, dim=10, rot_dim=6, vdim=14, q_rank=20, kv_rank=72, window=300, rot_dims=4), ("moe", 4, 2, 12))])
+    return None
+
+
 def named_config(name: str) -> dict:
+    cfg = _kutirax_named(name.lower())
+    if cfg is not None:
+        return cfg
     try:
         return qwen2_config(**NAMED_SIZES[name.lower()])
     except KeyError:
-        raise ValueError(f"unknown size name {name!r}; known: {sorted(NAMED_SIZES)}") from None
+        known = sorted(NAMED_SIZES) + ["kutirax-tiny-a", "kutirax-tiny-b", "kutirax-tiny-c"]
+        raise ValueError(f"unknown size name {name!r}; known: {known}") from None
