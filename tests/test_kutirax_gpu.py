@@ -150,6 +150,63 @@ def test_pair_norm_and_token_shift_kernels(dtype):
     assert float(state[1].abs().max()) == 0.0          # nobody's slot stays untouched
 
 
+@pytest.mark.parametrize("nh,rank,rot,rot_dims,window,page", [(5, 48, 16, 16, 33, 16), (16, 64, 32, 16, 7, 8), (3, 160, 16, 16, 400, 16),
+                                                             (7, 72, 6, 4, 20, 16), (4, 272, 32, 32, 1, 32)])
+def test_latent_attention_kernels(nh, rank, rot, rot_dims, window, page):
+    """The attention kernels alone over a hand-made paged cache of latents: three requests (a prompt portion that
+    continues 150 cached tokens, a single decoded token at position 400, a fresh prompt) against a plain 64-bit
+    computation from the same cache rows; the tensor-core kernel where it takes the shapes, the generic one always."""
+    from tokenmill_b200.kernels import ops
+    torch.manual_seed(nh)
+    D = rank + rot
+    starts, lens = [150, 400, 0], [37, 1, 70]
+    n_pages = sum(-(-(a + b) // page) for a, b in zip(starts, lens)) + 3
+    cache = (torch.randn(n_pages, page, 1, D) * 0.5).to(torch.bfloat16)
+    order = torch.randperm(n_pages).tolist()
+    width = max(-(-(a + b) // page) for a, b in zip(starts, lens))
+    table = np.zeros((3, width), dtype=np.int32)
+    for s in range(3):
+        for i in range(-(-(starts[s] + lens[s]) // page)):
+            table[s, i] = order.pop()
+    T = sum(lens)
+    q_lat = torch.randn(T, nh, rank)
+    q_rot = torch.randn(T, nh, rot).to(torch.bfloat16)
+    pos = np.concatenate([np.arange(a, a + b) for a, b in zip(starts, lens)])
+    half = rot_dims // 2
+    freq = 10000.0 ** (-2.0 * torch.arange(half, dtype=torch.float64) / rot_dims)
+    ang = torch.arange(512, dtype=torch.float64)[:, None] * freq
+    cos, sin = ang.cos().float(), ang.sin().float()
+    scale = 0.3
+    ref = torch.zeros(T, nh, rank, dtype=torch.float64)
+    t = 0
+    for s in range(3):
+        rows = torch.stack([cache[table[s, j // page], j % page, 0] for j in range(starts[s] + lens[s])]).double()
+        for i in range(lens[s]):
+            p = starts[s] + i
+            qr = pk.rotate_half(q_rot[t:t + 1].double(), torch.tensor([p]), 10000.0, rot_dims)[0]
+            q = torch.cat([q_lat[t].double(), qr], dim=-1)                      # [nh, D]
+            lo = max(0, p - window + 1)
+            sc = (q @ rows[lo:p + 1].T) * scale
+            ref[t] = torch.softmax(sc, -1) @ rows[lo:p + 1, :rank]
+            t += 1
+    t32 = lambda a: torch.as_tensor(np.asarray(a, dtype=np.int32), device=DEV)      # noqa: E731
+    cu = np.zeros(4, dtype=np.int32)
+    cu[1:] = np.cumsum(lens)
+    kinds = [(False, 32)] + ([(True, 64)] if ops.latent_attention_tc_ok(torch.bfloat16, rank, rot) else [])
+    assert len(kinds) == 2 or rank % 16 or rot % 16
+    for tc, tile in kinds:
+        per = [-(-n * nh // tile) for n in lens]
+        tile_seq = np.repeat(np.arange(3), per)
+        tile_row0 = np.concatenate([np.arange(k) * tile for k in per])
+        out = torch.zeros(nh, T, rank, dtype=torch.bfloat16, device=DEV)
+        ops.latent_attention(q_lat.to(DEV), q_rot.to(DEV), cos.to(DEV), sin.to(DEV), rot_dims, cache.to(DEV), t32(table),
+                             t32(cu), t32(starts), t32(tile_seq), t32(tile_row0), len(tile_seq), out.transpose(0, 1),
+                             scale=scale, window=window, tensor_cores=tc)
+        got = out.transpose(0, 1).float().cpu().double()
+        err = float((got - ref).abs().max())
+        assert err < 2e-2, (tc, err)
+
+
 @pytest.mark.parametrize("top,E", [(1, 5), (3, 12), (4, 4), (2, 37)])
 def test_router_kernel(top, E):
     from tokenmill_b200.kernels import ops

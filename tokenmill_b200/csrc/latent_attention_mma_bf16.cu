@@ -1,0 +1,276 @@
+// Attention over a cache of latents on the tensor cores (bfloat16 operands, 32-bit accumulation), for prompt
+// portions and decoded tokens alike. Same contract as tm_latent_attention (latent_attention.cu): every token's cache
+// row is [c (rank) | k_rot (rot)], a query row is [q_lat (rank) | rope(q_rot) (rot)], the score is their dot product
+// times scale over the last `window` positions, and the result is the softmax-weighted sum of the c rows.
+//
+// A block of four warps takes 64 consecutive (token, head) rows of one request (heads fastest, so a tile is a few
+// tokens times all heads and reads each cache row once for all of them) and one slice of up to NV * 8 result
+// columns; blocks with the same rows and another slice recompute the scores. Keys go in tiles of 32 anchored at
+// absolute positions 0, 32, ..., through a two-stage cp.async ring (rows outside the tile's key range are
+// zero-filled); S = Q K^T and O += P V are mma.sync.m16n8k16 with ldmatrix fragments (V is the first `rank`
+// columns of the same shared-memory tile, read transposed). Scores, the running maximum and sum, and the
+// rescaling are 32-bit; P is rounded to bfloat16 for the second product, q_lat for the first.
+// Shapes: rank and rot multiples of 16.
+#include "mma_util.cuh"
+
+namespace tmk {
+
+constexpr int kMlaRows = 64;
+constexpr int kMlaKeys = 32;
+
+template <int NV>   // result columns per block = NV * 8
+__global__ void __launch_bounds__(128) latent_attention_mma_kernel(
+    const float* __restrict__ q_lat, long long ql_stride_t, long long ql_stride_h,
+    const __nv_bfloat16* __restrict__ q_rot, long long qr_stride_t, long long qr_stride_h,
+    const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_dims,
+    const __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_table, int bt_stride,
+    const int* __restrict__ cu_q, const int* __restrict__ kv_before, const int* __restrict__ tile_seq,
+    const int* __restrict__ tile_row0, __nv_bfloat16* __restrict__ out, long long out_stride_t,
+    long long out_stride_h, int nh, int rank, int rot, int page_size, float scale, int window) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int D = rank + rot;
+  const int RS = D * 2 + 16;                                   // row stride in bytes: 8 rows fall into 8 different bank groups
+  unsigned char* qs = smem_raw;                                // [64][RS]
+  unsigned char* ks = qs + kMlaRows * RS;                      // 2 x [32][RS]
+
+  pdl_launch_dependents();
+  pdl_wait();
+  const int s = tile_seq[blockIdx.x];
+  const int row0 = tile_row0[blockIdx.x];
+  const int c0 = blockIdx.y * NV * 8;
+  const int q_start = cu_q[s];
+  const int q_len = cu_q[s + 1] - q_start;
+  const int before = kv_before[s];
+  const int n_rows = q_len * nh;
+  if (row0 >= n_rows) return;
+  const int row_end = min(row0 + kMlaRows, n_rows);
+  const int p_min = before + row0 / nh;
+  const int p_max = before + (row_end - 1) / nh;
+  const int j_lo = window > 0 ? max(0, p_min - window + 1) : 0;
+  const int j_hi = p_max;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int* table = block_table + (size_t)s * bt_stride;
+  const int half = rot_dims >> 1;
+  const int segs = D / 8;                                      // 16-byte pieces of a cache row
+
+  auto load_keys = [&](int kt, int stage) {
+    unsigned char* dst = ks + stage * (kMlaKeys * RS);
+    for (int idx = tid; idx < kMlaKeys * segs; idx += 128) {
+      const int jj = idx / segs, sg = idx - jj * segs;
+      const int j = kt + jj;
+      const bool ok = j >= j_lo && j <= j_hi;
+      const __nv_bfloat16* src = cache;
+      if (ok) src = cache + ((size_t)table[j / page_size] * page_size + (j % page_size)) * D + sg * 8;
+      cp_async16(smem_u32(dst + jj * RS + sg * 16), src, ok);
+    }
+    cp_async_commit();
+  };
+
+  const int kt0 = (j_lo / kMlaKeys) * kMlaKeys;
+  load_keys(kt0, 0);
+
+  // Stage the queries: the latent part rounded to bfloat16, the rotated part rotated in 32-bit first.
+  for (int idx = tid; idx < kMlaRows * D; idx += 128) {
+    const int r = idx / D, d = idx - r * D;
+    const int row = row0 + r;
+    float v = 0.f;
+    if (row < n_rows) {
+      const int tok = q_start + row / nh, head = row % nh;
+      if (d < rank) {
+        v = q_lat[(size_t)tok * ql_stride_t + (size_t)head * ql_stride_h + d];
+      } else {
+        const int i = d - rank;
+        const __nv_bfloat16* qr = q_rot + (size_t)tok * qr_stride_t + (size_t)head * qr_stride_h;
+        v = to_float(qr[i]);
+        const int pos = before + row / nh;
+        if (i < half) {
+          const float c = cos_t[(size_t)pos * half + i], sn = sin_t[(size_t)pos * half + i];
+          v = __fsub_rn(__fmul_rn(v, c), __fmul_rn(to_float(qr[i + half]), sn));
+        } else if (i < rot_dims) {
+          const float c = cos_t[(size_t)pos * half + i - half], sn = sin_t[(size_t)pos * half + i - half];
+          v = __fadd_rn(__fmul_rn(v, c), __fmul_rn(to_float(qr[i - half]), sn));
+        }
+      }
+    }
+    *reinterpret_cast<__nv_bfloat16*>(qs + r * RS + d * 2) = __float2bfloat16_rn(v);
+  }
+
+  // The two rows of this thread inside its warp's 16: g and g + 8.
+  const int g = lane >> 2, qd = lane & 3;
+  int p_row[2], lo_row[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int row = row0 + warp * 16 + g + 8 * i;
+    if (row < n_rows) {
+      p_row[i] = before + row / nh;
+      lo_row[i] = window > 0 ? max(0, p_row[i] - window + 1) : 0;
+    } else {
+      p_row[i] = -1;
+      lo_row[i] = 0;
+    }
+  }
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[NV][4];
+#pragma unroll
+  for (int n = 0; n < NV; ++n)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+
+  const uint32_t q_base = smem_u32(qs) + (warp * 16 + (lane & 15)) * RS + (lane >> 4) * 16;
+  const int mi = lane >> 3, lr = lane & 7;
+  const uint32_t k_off = ((mi >> 1) * 8 + lr) * RS + (mi & 1) * 16;        // S: matrices (keys 0-7 | 8-15) x (k 0-7 | 8-15)
+  const uint32_t v_off = ((mi & 1) * 8 + lr) * RS + (mi >> 1) * 16;        // O: matrices (keys 0-7 | 8-15) x (dims 0-7 | 8-15), transposed
+  const float sl2 = scale * 1.4426950408889634f;                           // scores kept in units of log2 e
+
+  int stage = 0;
+  for (int kt = kt0; kt <= j_hi; kt += kMlaKeys, stage ^= 1) {
+    if (kt + kMlaKeys <= j_hi) {
+      load_keys(kt + kMlaKeys, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint32_t k_base = smem_u32(ks + stage * (kMlaKeys * RS));
+
+    float sc[4][4];
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sc[n][e] = 0.f;
+    for (int kk = 0; kk < D; kk += 16) {
+      uint32_t a[4], b0, b1, b2, b3;
+      ldmatrix_x4(q_base + kk * 2, a[0], a[1], a[2], a[3]);
+      ldmatrix_x4(k_base + k_off + kk * 2, b0, b1, b2, b3);
+      mma_bf16_16816(sc[0], a, b0, b1);
+      mma_bf16_16816(sc[1], a, b2, b3);
+      ldmatrix_x4(k_base + 16 * RS + k_off + kk * 2, b0, b1, b2, b3);
+      mma_bf16_16816(sc[2], a, b0, b1);
+      mma_bf16_16816(sc[3], a, b2, b3);
+    }
+    // mask, online softmax (rows g and g + 8; a row's 32 scores lie in the four lanes of a quad)
+    float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = e >> 1;
+        const int j = kt + n * 8 + qd * 2 + (e & 1);
+        const bool ok = j >= j_lo && j <= j_hi && j <= p_row[i] && j >= lo_row[i];
+        sc[n][e] = ok ? sc[n][e] * sl2 : -INFINITY;
+        tmax[i] = fmaxf(tmax[i], sc[n][e]);
+      }
+    float corr[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 1));
+      tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 2));
+      const float m_new = fmaxf(m[i], tmax[i]);
+      corr[i] = m_new == -INFINITY ? 1.f : exp2f(m[i] - m_new);
+      m[i] = m_new;
+    }
+    float tsum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = e >> 1;
+        const float pv = m[i] == -INFINITY ? 0.f : exp2f(sc[n][e] - m[i]);
+        sc[n][e] = pv;
+        tsum[i] += pv;
+      }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      tsum[i] += __shfl_xor_sync(0xffffffffu, tsum[i], 1);
+      tsum[i] += __shfl_xor_sync(0xffffffffu, tsum[i], 2);
+      l[i] = l[i] * corr[i] + tsum[i];
+    }
+#pragma unroll
+    for (int n = 0; n < NV; ++n) {
+      o[n][0] *= corr[0]; o[n][1] *= corr[0];
+      o[n][2] *= corr[1]; o[n][3] *= corr[1];
+    }
+    uint32_t pa[2][4];
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+      pa[kk][0] = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
+      pa[kk][1] = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
+      pa[kk][2] = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+      pa[kk][3] = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+    }
+#pragma unroll
+    for (int dt = 0; dt < NV / 2; ++dt) {
+      if (c0 + dt * 16 < rank) {
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4_trans(k_base + kk * 16 * RS + v_off + (c0 + dt * 16) * 2, b0, b1, b2, b3);
+          mma_bf16_16816(o[2 * dt], pa[kk], b0, b1);
+          mma_bf16_16816(o[2 * dt + 1], pa[kk], b2, b3);
+        }
+      }
+    }
+    __syncthreads();               // the stage is free for the load after next
+  }
+
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int row = row0 + warp * 16 + g + 8 * i;
+    if (row >= n_rows) continue;
+    const int tok = q_start + row / nh, head = row % nh;
+    __nv_bfloat16* dst = out + (size_t)tok * out_stride_t + (size_t)head * out_stride_h;
+    const float inv = 1.0f / l[i];
+#pragma unroll
+    for (int n = 0; n < NV; ++n) {
+      const int d = c0 + n * 8 + qd * 2;
+      if (d < rank) {
+        const uint32_t v = pack_bf16(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+        *reinterpret_cast<uint32_t*>(dst + d) = v;
+      }
+    }
+  }
+}
+
+template <int NV>
+int launch_latent_mma(const float* q_lat, long long ql_t, long long ql_h, const void* q_rot, long long qr_t,
+                      long long qr_h, const float* cos_t, const float* sin_t, int rot_dims, const void* cache,
+                      const int* block_table, int bt_stride, const int* cu_q, const int* kv_before,
+                      const int* tile_seq, const int* tile_row0, int n_tiles, void* out, long long o_t, long long o_h,
+                      int nh, int rank, int rot, int page_size, float scale, int window, cudaStream_t stream) {
+  const int D = rank + rot;
+  const size_t smem = (size_t)(kMlaRows + 2 * kMlaKeys) * (D * 2 + 16);
+  if (smem > 220 * 1024) return TM_ERR_UNSUPPORTED_SHAPE;
+  auto kern = latent_attention_mma_kernel<NV>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const dim3 grid(n_tiles, (rank + NV * 8 - 1) / (NV * 8));
+  return launch_pdl(kern, grid, dim3(128), smem, stream, q_lat, ql_t, ql_h, (const __nv_bfloat16*)q_rot, qr_t, qr_h,
+                    cos_t, sin_t, rot_dims, (const __nv_bfloat16*)cache, block_table, bt_stride, cu_q, kv_before,
+                    tile_seq, tile_row0, (__nv_bfloat16*)out, o_t, o_h, nh, rank, rot, page_size, scale, window);
+}
+
+}  // namespace tmk
+
+// As tm_latent_attention, bfloat16 only, with tiles of 64 rows; rank and rot multiples of 16, even strides.
+extern "C" int tm_latent_attention_mma_bf16(const float* q_lat, long long ql_t, long long ql_h, const void* q_rot,
+                                            long long qr_t, long long qr_h, const float* cos_t, const float* sin_t,
+                                            int rot_dims, const void* cache, const int* block_table, int bt_stride,
+                                            const int* cu_q, const int* kv_before, const int* tile_seq,
+                                            const int* tile_row0, int n_tiles, void* out, long long o_t, long long o_h,
+                                            int nh, int rank, int rot, int page_size, float scale, int window,
+                                            cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (rank % 16 || rot % 16 || (o_t & 1) || (o_h & 1) || (reinterpret_cast<uintptr_t>(out) & 3) ||
+      (reinterpret_cast<uintptr_t>(cache) & 15))
+    return TM_ERR_UNSUPPORTED_SHAPE;
+#define TM_MLA(NV)                                                                                                   \
+  return tmk::launch_latent_mma<NV>(q_lat, ql_t, ql_h, q_rot, qr_t, qr_h, cos_t, sin_t, rot_dims, cache, block_table, \
+                                    bt_stride, cu_q, kv_before, tile_seq, tile_row0, n_tiles, out, o_t, o_h, nh, rank, \
+                                    rot, page_size, scale, window, stream)
+  if (rank <= 64) TM_MLA(8);
+  if (rank <= 128) TM_MLA(16);
+  TM_MLA(32);
+#undef TM_MLA
+}

@@ -854,12 +854,22 @@ def latent_prepare(proj: torch.Tensor, q_rank: int, rank: int, rot: int, rot_dim
              _tc_flag(proj.device).data_ptr(), _stream())
 
 
+def latent_attention_tc_ok(dtype: torch.dtype, rank: int, rot: int) -> bool:
+    """Whether the tensor-core kernel takes these shapes (bfloat16, both parts of a cache row multiples of 16 wide)."""
+    return dtype == torch.bfloat16 and rank % 16 == 0 and rot % 16 == 0 and \
+        os.environ.get("TOKENMILL_LATENT_TC", "1") != "0"
+
+
+LATENT_TC_TILE_ROWS, LATENT_TILE_ROWS = 64, 32
+
+
 def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, rot_dims: int,
                      cache: torch.Tensor, block_table: torch.Tensor, cu_q: torch.Tensor, kv_before: torch.Tensor,
                      tile_seq: torch.Tensor, tile_row0: torch.Tensor, n_tiles: int, out: torch.Tensor, *, scale: float,
-                     window: int) -> torch.Tensor:
+                     window: int, tensor_cores: bool = False) -> torch.Tensor:
     """q_lat [T, nh, rank] float32, q_rot [T, nh, rot] (unrotated), out [T, nh, rank]: any strides with a unit last
-    one; cache [pages, page, 1, rank + rot]."""
+    one; cache [pages, page, 1, rank + rot]. Tiles of 32 (token, head) rows, or of 64 with ``tensor_cores``
+    (bfloat16, mma.sync; see ``latent_attention_tc_ok``)."""
     T, nh, rank = q_lat.shape
     rot = q_rot.shape[2]
     dt = cache.dtype
@@ -869,6 +879,16 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, cos: torch.Tensor
     if q_lat.dtype != torch.float32 or q_rot.dtype != dt or out.dtype != dt or out.shape != q_lat.shape or \
             cache.shape[-1] != rank + rot or cos.shape[1] * 2 != rot_dims:
         raise lib.KernelError("latent_attention: dtypes or shapes do not fit")
+    if tensor_cores:
+        if not latent_attention_tc_ok(dt, rank, rot):
+            raise lib.KernelError("latent_attention: the tensor-core kernel takes bfloat16 with rank and rot multiples of 16")
+        lib.call("tm_latent_attention_mma_bf16", q_lat.data_ptr(), q_lat.stride(0), q_lat.stride(1), q_rot.data_ptr(),
+                 q_rot.stride(0), q_rot.stride(1), _req(cos, "cos", torch.float32), _req(sin, "sin", torch.float32), rot_dims,
+                 _req(cache, "cache"), _req(block_table, "block_table", torch.int32), block_table.stride(0),
+                 _req(cu_q, "cu_q", torch.int32), _req(kv_before, "kv_before", torch.int32),
+                 _req(tile_seq, "tile_seq", torch.int32), _req(tile_row0, "tile_row0", torch.int32), n_tiles, out.data_ptr(),
+                 out.stride(0), out.stride(1), nh, rank, rot, cache.shape[1], float(scale), int(window), _stream())
+        return out
     lib.call("tm_latent_attention", _code(dt), q_lat.data_ptr(), q_lat.stride(0), q_lat.stride(1), q_rot.data_ptr(),
              q_rot.stride(0), q_rot.stride(1), _req(cos, "cos", torch.float32), _req(sin, "sin", torch.float32), rot_dims,
              _req(cache, "cache"), _req(block_table, "block_table", torch.int32), block_table.stride(0),

@@ -23,7 +23,6 @@ import torch
 
 from ..kernels import ops
 from ..registry import get_part, register_mixer
-from .attention_plan import tiles_for
 from .base import LayerCache, StepInputs, StepMetadata, StepShape, part_limit_positions, part_max_positions
 from .spec import PagedKVNeed, PartSpec, StateNeed, WeightSpec
 
@@ -47,6 +46,10 @@ class LatentAttention:
         # checkpoint names of the tensors, relative to the mixer's prefix
         self.names = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk",
                       "uv": "uv", "o": "o", **(names or {})}
+        # bfloat16 with both parts of a cache row multiples of 16 wide: tensor cores; anything else (and the 32-bit
+        # path): the shape-generic kernel on CUDA cores
+        self.tensor_cores = ops.latent_attention_tc_ok(dtype, kv_rank, rot_dim)
+        self.tile_rows = ops.LATENT_TC_TILE_ROWS if self.tensor_cores else ops.LATENT_TILE_ROWS
         self.w_down = self.w_uq = self.w_uk_t = self.w_uv = self.w_o = None
         self.g_q = self.g_kv = self.cos = self.sin = None
 
@@ -92,11 +95,14 @@ class LatentAttention:
     # --- per-step work list -----------------------------------------------------------------------------------
 
     def metadata_key(self):
-        return ("latent_attention", self.nh)
+        return ("latent_attention", self.nh, self.tile_rows)
 
     def step_metadata(self, shape: StepShape) -> StepMetadata:
-        """Row tiles of the attention kernel: 32 (token, head) rows of one request each."""
-        tile_seq, tile_row0 = tiles_for(shape.q_lens, self.nh)
+        """Row tiles of the attention kernel: ``tile_rows`` consecutive (token, head) rows of one request each."""
+        per_seq = (shape.q_lens.astype(np.int64) * self.nh + self.tile_rows - 1) // self.tile_rows
+        tile_seq = np.repeat(np.arange(len(per_seq), dtype=np.int32), per_seq)
+        first = np.cumsum(per_seq) - per_seq
+        tile_row0 = ((np.arange(tile_seq.size) - np.repeat(first, per_seq)) * self.tile_rows).astype(np.int32)
         return StepMetadata({"tile_seq": tile_seq, "tile_row0": tile_row0}, {"n_tiles": int(tile_seq.size)},
                             constant_in_graph=True)
 
@@ -111,16 +117,13 @@ class LatentAttention:
                            step.positions, self.cos, self.sin, slot_map, cq, cache.k)
         q = ops.linear(cq, self.w_uq).view(T, nh, self.dn + self.dr)
         q_lat = torch.empty((nh, T, self.rank), dtype=torch.float32, device=dev)
-        if self.dtype == torch.float32:
-            ops.bmm_nt(q[:, :, :self.dn].transpose(0, 1), self.w_uk_t, q_lat)
-        else:
-            ops.bmm_nt(q[:, :, :self.dn].transpose(0, 1), self.w_uk_t, q_lat)
+        ops.bmm_nt(q[:, :, :self.dn].transpose(0, 1), self.w_uk_t, q_lat)
         meta = step.meta[self.metadata_key()]
         o_lat = torch.empty((nh, T, self.rank), dtype=self.dtype, device=dev)
         ops.latent_attention(q_lat.transpose(0, 1), q[:, :, self.dn:], self.cos, self.sin, self.rot_dims, cache.k,
                              step.block_tables[cache.group], step.cu_q, step.kv_before, meta.arrays["tile_seq"],
                              meta.arrays["tile_row0"], meta.host["n_tiles"], o_lat.transpose(0, 1), scale=self.scale,
-                             window=self.window)
+                             window=self.window, tensor_cores=self.tensor_cores)
         heads = torch.empty((T, nh, self.dv), dtype=self.dtype, device=dev)
         ops.bmm_nt(o_lat, self.w_uv, heads.transpose(0, 1))
         return ops.linear(heads.view(T, nh * self.dv), self.w_o)
