@@ -27,6 +27,10 @@ chunked prefill with a 2,048-token budget; ``7b-prefix``: Qwen2.5-7B sizes, cont
 4,096-token prompts that share their first 1,024 tokens, 512 new tokens, prefix caching, a pool too small for
 all of them so that requests are preempted.
 
+``--design kutirax [--design-sizes s|m] [--kernels]`` measures the Kutirax design (latent attention with a window,
+state-space layers, experts) beside Qwen2 at the same width, depth and vocabulary: one 2,048-token prompt and decode
+steps of 8 and 32 requests, and with ``--kernels`` the device time by kernel name of one step of each kind.
+
 The engine runs on one GPU: for --gpus N > 1 a line says so and the exit code is 2.
 """
 
@@ -708,6 +712,121 @@ def run_reference(args) -> dict:
     }
 
 
+# --- another design beside the closest existing model, at equal width and depth (--design kutirax) ---------------
+
+DESIGN_SIZES = {
+    # width, then the Kutirax layers' sizes, then the Qwen2 layer of the same width it is measured beside
+    "s": dict(width=1024,
+              latent=dict(heads=8, dim=64, rot_dim=32, vdim=64, q_rank=384, kv_rank=256, window=512),
+              mamba=dict(heads=32, vdim=64, state=64, groups=4, conv=4, norm_groups=4),
+              dense=4096, moe=(16, 2, 1024),
+              qwen=dict(num_attention_heads=8, num_key_value_heads=2, head_dim=128, intermediate_size=2816)),
+    "m": dict(width=2048,
+              latent=dict(heads=16, dim=128, rot_dim=64, vdim=128, q_rank=768, kv_rank=512, window=1024),
+              mamba=dict(heads=64, vdim=64, state=128, groups=8, conv=4, norm_groups=8),
+              dense=8192, moe=(32, 4, 1024),
+              qwen=dict(num_attention_heads=16, num_key_value_heads=2, head_dim=128, intermediate_size=5632)),
+}
+
+
+def design_model_dirs(size: str, vocab: int):
+    """(Kutirax folder, Qwen2 folder, description): four layers each, random weights, the same width and vocabulary.
+    Kutirax: state-space + dense, latent attention + experts (twice), state-space + experts."""
+    from tokenmill_b200.weights import qwen2_config, write_random_model
+    from tokenmill_b200.weights.random_init import kutirax_config, kutirax_latent, kutirax_mamba
+    z = DESIGN_SIZES[size]
+    lat, mam, moe = kutirax_latent(**z["latent"]), kutirax_mamba(**z["mamba"]), ("moe", *z["moe"])
+    kcfg = kutirax_config(vocab=vocab, width=z["width"], eps=1e-5, residual_mult=0.5, layers=[
+        ("mamba2", mam, ("dense", z["dense"])), ("latent_attention", lat, moe), ("latent_attention", lat, moe),
+        ("mamba2", mam, moe)])
+    qcfg = qwen2_config(vocab_size=vocab, hidden_size=z["width"], num_hidden_layers=4, rope_theta=1000000.0,
+                        rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=32768, **z["qwen"])
+    dirs = []
+    for name, cfg in (("kutirax", kcfg), ("qwen2", qcfg)):
+        tmp = tempfile.TemporaryDirectory(prefix=f"tokenmill_bench_{name}_")
+        t0 = time.time()
+        write_random_model(tmp.name, cfg, seed=0)
+        print(f"[bench] random {name} weights written in {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
+        dirs.append(tmp)
+    return dirs[0], dirs[1], z
+
+
+def kernel_table(engine, tokens: int, batch: int) -> dict:
+    """Device time by kernel name for one prompt step of ``tokens`` tokens and one decode step of ``batch`` requests
+    (launch by launch, no graph), from the profiler's CUDA activity records. A profiling aid: these times are taken
+    under the profiler and are for shares, not for the numbers reported."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from tokenmill_b200.engine.batch import StepEntry
+    runner, cache = engine.runner, engine.cache
+    out = {}
+    p = prompts(max(batch, 1), tokens, seed=3)
+    for what in ("prefill", "decode"):
+        handles = []
+        if what == "decode":
+            for q in p[:batch]:
+                h = cache.new_handle()
+                cache.allocate(h, q[:512] + [0])
+                runner.step([StepEntry(h, q[:512], 0, [])])
+                handles.append(h)
+            entries = [StepEntry(h, [7], 512, [0]) for h in handles]
+        else:
+            h = cache.new_handle()
+            cache.allocate(h, p[0])
+            handles.append(h)
+            entries = [StepEntry(h, p[0], 0, [tokens - 1])]
+        torch.cuda.synchronize()
+        graphs, runner.graph_max_batch = runner.graph_max_batch, 0
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            runner.step(entries)
+            torch.cuda.synchronize()
+        runner.graph_max_batch = graphs
+        rows = sorted(((e.key, e.device_time_total, e.count) for e in prof.key_averages() if e.device_time_total > 0),
+                      key=lambda r: -r[1])
+        total = sum(r[1] for r in rows)
+        out[what] = {"total_us": round(total, 1), "kernels": [{"name": k[:90], "us": round(t, 1), "n": n} for k, t, n in rows[:14]]}
+        for h in handles:
+            cache.free(h)
+    return out
+
+
+def run_design(args) -> dict:
+    """Prompt and decode throughput of Kutirax beside Qwen2 at the same width, depth and vocabulary (random weights):
+    one 2,048-token prompt; decode steps of 8 and of 32 requests behind 512-token prompts, in captured graphs."""
+    import torch
+    from tokenmill_b200 import EngineConfig
+    from tokenmill_b200.engine import LLMEngine
+    global NEW_TOKENS
+    vocab = SIZES["vocab_size"]
+    kdir, qdir, z = design_model_dirs(args.design_sizes, vocab)
+    result = {"design": "Kutirax", "beside": "Qwen2", "sizes": args.design_sizes, "width": z["width"], "layers": 4,
+              "dtype": "bfloat16", "data": "synthetic", "prefill_tokens": args.prefill_tokens, "points": {}}
+    sampler = ClockSampler()
+    sampler.start()
+    try:
+        for name, folder in (("kutirax", kdir.name), ("qwen2", qdir.name)):
+            cfg = EngineConfig(model=folder, dtype="bfloat16", block_size=PAGE, max_model_len=4096, max_num_seqs=64,
+                               max_num_batched_tokens=4096, kv_cache_mb=3072, watermark=0.0, cuda_graphs=not args.no_graphs,
+                               cuda_graph_max_batch=64)
+            engine = LLMEngine(cfg)
+            pf = prefill_timed(engine, args.prefill_tokens, reps=5)
+            point = {"prefill_ms": round(pf["ms"], 3), "prefill_tok_s": round(args.prefill_tokens / (pf["ms"] / 1e3), 1)}
+            for batch in (8, 32):
+                d = decode_device_timed(engine, batch, args.steps, args.warmup, skip_ahead=False, prompt_len=512)
+                point[f"decode_b{batch}_ms"] = round(d["ms_per_step"], 4)
+                point[f"decode_b{batch}_tok_s"] = round(d["tok_s"], 1)
+            if args.kernels:
+                point["kernels"] = kernel_table(engine, args.prefill_tokens, 8)
+            result["points"][name] = point
+            del engine
+            torch.cuda.empty_cache()
+    finally:
+        result["clocks"] = sampler.stop()
+        kdir.cleanup()
+        qdir.cleanup()
+    return result
+
+
 def main() -> int:
     global PROMPT_LEN, CONTEXT
     ap = argparse.ArgumentParser()
@@ -725,6 +844,10 @@ def main() -> int:
                     help="profiling aid with --only decode_b<batch>: prompts of this many tokens instead of 512")
     ap.add_argument("--no-skip", action="store_true", help="profiling aid: time the decode steps right behind the prompt")
     ap.add_argument("--no-fp32", action="store_true", help="leave out the float32 engine's points")
+    ap.add_argument("--design", default="", choices=["", "kutirax"],
+                    help="measure another design beside Qwen2 at equal width and depth instead of the headline bench")
+    ap.add_argument("--design-sizes", default="s", choices=sorted(DESIGN_SIZES), help="with --design: which layer sizes")
+    ap.add_argument("--kernels", action="store_true", help="with --design: add device time by kernel name (profiler)")
     ap.add_argument("--workload", default="", choices=["", *WORKLOADS],
                     help="run one of the other baseline workloads through LLMEngine instead of the headline bench")
     args = ap.parse_args()
@@ -742,7 +865,9 @@ def main() -> int:
         PROMPT_LEN, CONTEXT = args.prompt_len, max(CONTEXT, args.prompt_len + NEW_TOKENS + 64)
     if args.only == "prefill":
         CONTEXT = max(CONTEXT, args.prefill_tokens + 64)
-    if args.workload:
+    if args.design:
+        result = run_design(args)
+    elif args.workload:
         result = run_workload(args)
     else:
         result = run_reference(args) if args.impl == "reference" else run_ours(args)

@@ -192,19 +192,21 @@ def test_latent_attention_kernels(nh, rank, rot, rot_dims, window, page):
     t32 = lambda a: torch.as_tensor(np.asarray(a, dtype=np.int32), device=DEV)      # noqa: E731
     cu = np.zeros(4, dtype=np.int32)
     cu[1:] = np.cumsum(lens)
-    kinds = [(False, 32)] + ([(True, 64)] if ops.latent_attention_tc_ok(torch.bfloat16, rank, rot) else [])
-    assert len(kinds) == 2 or rank % 16 or rot % 16
-    for tc, tile in kinds:
+    kinds = [(False, 32, 1)] + ([(True, 64, 1), (True, 64, 3), (True, 64, 40)]
+                                if ops.latent_attention_tc_ok(torch.bfloat16, rank, rot) else [])
+    assert len(kinds) == 4 or rank % 16 or rot % 16
+    for tc, tile, splits in kinds:
         per = [-(-n * nh // tile) for n in lens]
         tile_seq = np.repeat(np.arange(3), per)
         tile_row0 = np.concatenate([np.arange(k) * tile for k in per])
         out = torch.zeros(nh, T, rank, dtype=torch.bfloat16, device=DEV)
+        part = torch.full((len(tile_seq) * splits * 64 * (rank + 2),), float("nan"), device=DEV) if splits > 1 else None
         ops.latent_attention(q_lat.to(DEV), q_rot.to(DEV), cos.to(DEV), sin.to(DEV), rot_dims, cache.to(DEV), t32(table),
                              t32(cu), t32(starts), t32(tile_seq), t32(tile_row0), len(tile_seq), out.transpose(0, 1),
-                             scale=scale, window=window, tensor_cores=tc)
+                             scale=scale, window=window, tensor_cores=tc, n_splits=splits, part=part)
         got = out.transpose(0, 1).float().cpu().double()
         err = float((got - ref).abs().max())
-        assert err < 2e-2, (tc, err)
+        assert err < 2e-2, (tc, splits, err)
 
 
 @pytest.mark.parametrize("top,E", [(1, 5), (3, 12), (4, 4), (2, 37)])
@@ -374,10 +376,29 @@ def test_a_far_key_and_an_old_state_show(kutirax_dirs, tmp_path):
     changed = list(reqs["r0"])
     changed[3] = (changed[3] + 1) % cfg["vocab"]
     assert (pk.forward(cfg, w, changed).float()[-1] - plain["r0"][-1]).abs().max() > 20 * tol      # the state remembers
-    for mode in ("tail", "mixed"):
-        steps, max_tokens = tail_decode_steps(reqs, tail=120) if mode == "tail" else mixed_steps(reqs, seed=3)
+    for mode in ("whole", "tail", "mixed"):       # (portions of 256 tokens and more run the recurrence over time slices)
+        steps, max_tokens = tail_decode_steps(reqs, tail=120) if mode == "tail" else _steps(mode, reqs) if mode == "whole" \
+            else mixed_steps(reqs, seed=3)
         outputs = run_trace(folder, "float32", steps, max_tokens, tmp_path / mode)
         check_against_plain(steps, outputs, reqs, plain, "float32")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_time_sliced_recurrence_under_every_cut(kutirax_dirs, dtype, tmp_path, plain_cache, monkeypatch):
+    """The three-pass recurrence over time slices, switched on for portions from 12 tokens with slices of 8: whole
+    prompts, portions and mixed batches (requests of one token beside requests of many slices, last slices that
+    are not full) against the plain recurrence."""
+    from tokenmill_b200.parts import state_space
+    monkeypatch.setattr(state_space, "SLICED_FROM", 12)
+    monkeypatch.setattr(state_space, "SLICE_LEN", 8)
+    for size in ("kutirax-tiny-a", "kutirax-tiny-c"):
+        folder = kutirax_dirs[size]
+        vocab = json.loads((folder / "config.json").read_text())["vocab"]
+        reqs = make_requests(vocab, LENGTHS, seed=11)
+        for mode in ("whole", "portions", "mixed"):
+            steps, max_tokens = _steps(mode, reqs)
+            outputs = run_trace(folder, dtype, steps, max_tokens, tmp_path / f"{size}_{mode}")
+            _check(steps, outputs, reqs, _plain(folder, reqs, plain_cache), dtype)
 
 
 def test_slots_and_pages_used_again_start_clean(kutirax_dirs, tmp_path, plain_cache):

@@ -10,6 +10,9 @@
 // zero-filled); S = Q K^T and O += P V are mma.sync.m16n8k16 with ldmatrix fragments (V is the first `rank`
 // columns of the same shared-memory tile, read transposed). Scores, the running maximum and sum, and the
 // rescaling are 32-bit; P is rounded to bfloat16 for the second product, q_lat for the first.
+// With n_splits > 1 (steps of few rows, where row tiles alone would leave most multiprocessors idle) a tile's key
+// tiles are dealt out in n_splits contiguous runs over blockIdx.z; each block writes its unnormalised sums with
+// their maximum and weight to scratch, and tm_latent_attention_combine merges the runs in index order.
 // Shapes: rank and rot multiples of 16.
 #include "mma_util.cuh"
 
@@ -26,7 +29,8 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     const __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_table, int bt_stride,
     const int* __restrict__ cu_q, const int* __restrict__ kv_before, const int* __restrict__ tile_seq,
     const int* __restrict__ tile_row0, __nv_bfloat16* __restrict__ out, long long out_stride_t,
-    long long out_stride_h, int nh, int rank, int rot, int page_size, float scale, int window) {
+    long long out_stride_h, int nh, int rank, int rot, int page_size, float scale, int window, int n_splits,
+    float* __restrict__ part) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int D = rank + rot;
   const int RS = D * 2 + 16;                                   // row stride in bytes: 8 rows fall into 8 different bank groups
@@ -66,8 +70,15 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     cp_async_commit();
   };
 
-  const int kt0 = (j_lo / kMlaKeys) * kMlaKeys;
-  load_keys(kt0, 0);
+  int kt0 = (j_lo / kMlaKeys) * kMlaKeys;
+  int kt_last = (j_hi / kMlaKeys) * kMlaKeys;
+  if (n_splits > 1) {                                          // this block's run of the tile's key tiles (maybe empty)
+    const int n_kt = (kt_last - kt0) / kMlaKeys + 1;
+    const int per = (n_kt + n_splits - 1) / n_splits;
+    kt0 += blockIdx.z * per * kMlaKeys;
+    kt_last = min(kt_last, kt0 + (per - 1) * kMlaKeys);
+  }
+  if (kt0 <= kt_last) load_keys(kt0, 0);
 
   // Stage the queries: the latent part rounded to bfloat16, the rotated part rotated in 32-bit first.
   for (int idx = tid; idx < kMlaRows * D; idx += 128) {
@@ -123,8 +134,8 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
   const float sl2 = scale * 1.4426950408889634f;                           // scores kept in units of log2 e
 
   int stage = 0;
-  for (int kt = kt0; kt <= j_hi; kt += kMlaKeys, stage ^= 1) {
-    if (kt + kMlaKeys <= j_hi) {
+  for (int kt = kt0; kt <= kt_last; kt += kMlaKeys, stage ^= 1) {
+    if (kt + kMlaKeys <= kt_last) {
       load_keys(kt + kMlaKeys, stage ^ 1);
       cp_async_wait<1>();
     } else {
@@ -213,6 +224,25 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     __syncthreads();               // the stage is free for the load after next
   }
 
+  if (n_splits > 1) {
+    // scratch: [tile][split][64 rows][rank + 2] floats: unnormalised sums, then maximum (log2 units) and weight
+    const int W = rank + 2;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = warp * 16 + g + 8 * i;
+      float* dst = part + (((size_t)blockIdx.x * n_splits + blockIdx.z) * kMlaRows + r) * W;
+#pragma unroll
+      for (int n = 0; n < NV; ++n) {
+        const int d = c0 + n * 8 + qd * 2;
+        if (d < rank) *reinterpret_cast<float2*>(dst + d) = make_float2(o[n][2 * i], o[n][2 * i + 1]);
+      }
+      if (qd == 0 && blockIdx.y == 0) {
+        dst[rank] = m[i];
+        dst[rank + 1] = l[i];
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int row = row0 + warp * 16 + g + 8 * i;
@@ -231,12 +261,49 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
   }
 }
 
+// One block per row tile, a warp per 8 rows: merge the runs of a row in index order.
+__global__ void __launch_bounds__(256) latent_attention_combine_kernel(
+    const float* __restrict__ part, int n_splits, const int* __restrict__ cu_q, const int* __restrict__ tile_seq,
+    const int* __restrict__ tile_row0, __nv_bfloat16* __restrict__ out, long long out_stride_t, long long out_stride_h,
+    int nh, int rank) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int s = tile_seq[blockIdx.x], row0 = tile_row0[blockIdx.x];
+  const int q_start = cu_q[s], n_rows = (cu_q[s + 1] - q_start) * nh;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int W = rank + 2;
+  for (int r = warp; r < kMlaRows; r += 8) {
+    const int row = row0 + r;
+    if (row >= n_rows) break;
+    const float* base = part + ((size_t)blockIdx.x * n_splits * kMlaRows + r) * W;
+    float mx = -INFINITY;
+    for (int z = 0; z < n_splits; ++z) mx = fmaxf(mx, base[(size_t)z * kMlaRows * W + rank]);
+    float lsum = 0.f;
+    for (int z = 0; z < n_splits; ++z) {
+      const float* p = base + (size_t)z * kMlaRows * W;
+      if (p[rank] != -INFINITY) lsum += p[rank + 1] * exp2f(p[rank] - mx);
+    }
+    const float inv = 1.0f / lsum;
+    const int tok = q_start + row / nh, head = row % nh;
+    __nv_bfloat16* dst = out + (size_t)tok * out_stride_t + (size_t)head * out_stride_h;
+    for (int d = lane; d < rank; d += 32) {
+      float a = 0.f;
+      for (int z = 0; z < n_splits; ++z) {
+        const float* p = base + (size_t)z * kMlaRows * W;
+        if (p[rank] != -INFINITY) a = fmaf(p[d], exp2f(p[rank] - mx), a);
+      }
+      dst[d] = __float2bfloat16_rn(a * inv);
+    }
+  }
+}
+
 template <int NV>
 int launch_latent_mma(const float* q_lat, long long ql_t, long long ql_h, const void* q_rot, long long qr_t,
                       long long qr_h, const float* cos_t, const float* sin_t, int rot_dims, const void* cache,
                       const int* block_table, int bt_stride, const int* cu_q, const int* kv_before,
                       const int* tile_seq, const int* tile_row0, int n_tiles, void* out, long long o_t, long long o_h,
-                      int nh, int rank, int rot, int page_size, float scale, int window, cudaStream_t stream) {
+                      int nh, int rank, int rot, int page_size, float scale, int window, int n_splits, float* part,
+                      cudaStream_t stream) {
   const int D = rank + rot;
   const size_t smem = (size_t)(kMlaRows + 2 * kMlaKeys) * (D * 2 + 16);
   if (smem > 220 * 1024) return TM_ERR_UNSUPPORTED_SHAPE;
@@ -245,30 +312,36 @@ int launch_latent_mma(const float* q_lat, long long ql_t, long long ql_h, const 
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  const dim3 grid(n_tiles, (rank + NV * 8 - 1) / (NV * 8));
-  return launch_pdl(kern, grid, dim3(128), smem, stream, q_lat, ql_t, ql_h, (const __nv_bfloat16*)q_rot, qr_t, qr_h,
-                    cos_t, sin_t, rot_dims, (const __nv_bfloat16*)cache, block_table, bt_stride, cu_q, kv_before,
-                    tile_seq, tile_row0, (__nv_bfloat16*)out, o_t, o_h, nh, rank, rot, page_size, scale, window);
+  const dim3 grid(n_tiles, (rank + NV * 8 - 1) / (NV * 8), n_splits);
+  const int st = launch_pdl(kern, grid, dim3(128), smem, stream, q_lat, ql_t, ql_h, (const __nv_bfloat16*)q_rot, qr_t,
+                            qr_h, cos_t, sin_t, rot_dims, (const __nv_bfloat16*)cache, block_table, bt_stride, cu_q,
+                            kv_before, tile_seq, tile_row0, (__nv_bfloat16*)out, o_t, o_h, nh, rank, rot, page_size,
+                            scale, window, n_splits, part);
+  if (st != 0 || n_splits <= 1) return st;
+  return launch_pdl(latent_attention_combine_kernel, dim3(n_tiles), dim3(256), 0, stream, (const float*)part, n_splits,
+                    cu_q, tile_seq, tile_row0, (__nv_bfloat16*)out, o_t, o_h, nh, rank);
 }
 
 }  // namespace tmk
 
 // As tm_latent_attention, bfloat16 only, with tiles of 64 rows; rank and rot multiples of 16, even strides.
+// n_splits > 1: part holds n_tiles * n_splits * 64 * (rank + 2) floats.
 extern "C" int tm_latent_attention_mma_bf16(const float* q_lat, long long ql_t, long long ql_h, const void* q_rot,
                                             long long qr_t, long long qr_h, const float* cos_t, const float* sin_t,
                                             int rot_dims, const void* cache, const int* block_table, int bt_stride,
                                             const int* cu_q, const int* kv_before, const int* tile_seq,
                                             const int* tile_row0, int n_tiles, void* out, long long o_t, long long o_h,
                                             int nh, int rank, int rot, int page_size, float scale, int window,
-                                            cudaStream_t stream) {
+                                            int n_splits, float* part, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  if (n_splits < 1 || n_splits > 65535 || (n_splits > 1 && part == nullptr)) return TM_ERR_SCRATCH_TOO_SMALL;
   if (rank % 16 || rot % 16 || (o_t & 1) || (o_h & 1) || (reinterpret_cast<uintptr_t>(out) & 3) ||
       (reinterpret_cast<uintptr_t>(cache) & 15))
     return TM_ERR_UNSUPPORTED_SHAPE;
 #define TM_MLA(NV)                                                                                                   \
   return tmk::launch_latent_mma<NV>(q_lat, ql_t, ql_h, q_rot, qr_t, qr_h, cos_t, sin_t, rot_dims, cache, block_table, \
                                     bt_stride, cu_q, kv_before, tile_seq, tile_row0, n_tiles, out, o_t, o_h, nh, rank, \
-                                    rot, page_size, scale, window, stream)
+                                    rot, page_size, scale, window, n_splits, part, stream)
   if (rank <= 64) TM_MLA(8);
   if (rank <= 128) TM_MLA(16);
   TM_MLA(32);

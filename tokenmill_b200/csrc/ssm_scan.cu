@@ -13,8 +13,17 @@
 //   dt = softplus(dt_raw + dt_bias[h])        a = exp(-exp(A_log[h]) * dt)
 //   S <- a * S + dt * B_t x_t^T               y_t = S^T C_t + D[h] * x_t
 // One block per (head, request, slice of vdim); each of a block's columns p is served by 8 lanes that hold N / 8
-// state values each in registers for the whole step. Tokens are taken in chunks of 16 through shared memory and
+// state values each in registers for the whole step. Tokens are taken in chunks through shared memory and
 // walked strictly in order, so the result does not depend on how a request was cut into steps.
+//
+// A long prompt portion would leave one block per (head, request) walking thousands of tokens one after the other
+// (about 0.4 us a token). Such steps run in three passes over time slices of `slice_len` tokens instead
+// (tm_ssm_scan with mode 1, tm_ssm_pass_states, tm_ssm_scan with mode 2): every slice first runs the recurrence
+// from a zero state (all slices at once) and leaves its end state and the product of its decays; a small kernel
+// walks each request's slices in order, S_start[k+1] = a[k] S_start[k] + S_local[k], and writes the request's new
+// state; then every slice runs again from its true start state and writes y. Twice the arithmetic, a slice's
+// length of sequential steps instead of the portion's; the result differs from the token-by-token walk by 32-bit
+// rounding only.
 #include "common.cuh"
 
 namespace tmk {
@@ -71,7 +80,6 @@ __global__ void __launch_bounds__(256) conv_silu_state_kernel(
 }
 
 constexpr int kScanLanes = 8;        // lanes that share one column of the state
-constexpr int kScanChunk = 16;       // tokens staged at a time
 
 __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 
@@ -80,33 +88,43 @@ __global__ void __launch_bounds__(512) ssm_scan_kernel(
     const T* __restrict__ xbc, int channels, const T* __restrict__ proj, long long proj_stride, int dt_col,
     const float* __restrict__ A_log, const float* __restrict__ dt_bias, const float* __restrict__ Dskip,
     float* __restrict__ state, long long state_stride, long long state_off, const int* __restrict__ cu_q,
-    const int* __restrict__ state_slots, float* __restrict__ y, int heads, int vdim, int N, int groups, int cols) {
+    const int* __restrict__ state_slots, float* __restrict__ y, int heads, int vdim, int N, int groups, int cols,
+    int chunk, int mode, int slice_len, int max_slices, float* __restrict__ slice_S, float* __restrict__ slice_a) {
   extern __shared__ __align__(16) float sm[];
   float* Bs = sm;                               // [chunk][N]
-  float* Cs = Bs + kScanChunk * N;              // [chunk][N]
-  float* xs = Cs + kScanChunk * N;              // [chunk][cols]
-  float* dts = xs + kScanChunk * cols;          // [chunk]
-  float* decs = dts + kScanChunk;               // [chunk]
+  float* Cs = Bs + chunk * N;                   // [chunk][N]
+  float* xs = Cs + chunk * N;                   // [chunk][cols]
+  float* dts = xs + chunk * cols;               // [chunk]
+  float* decs = dts + chunk;                    // [chunk]
   pdl_launch_dependents();
   pdl_wait();
-  const int h = blockIdx.x, s = blockIdx.y, p0 = blockIdx.z * cols;
+  const int h = blockIdx.x, p0 = blockIdx.z * cols;
+  const int s = mode == 0 ? blockIdx.y : blockIdx.y / max_slices;
+  const int slice = mode == 0 ? 0 : blockIdx.y % max_slices;
   const int g = h / (heads / groups);
   const int inner = heads * vdim;
   const int tid = threadIdx.x;
   const int r = tid & (kScanLanes - 1), pl = tid / kScanLanes;
   const int p = p0 + pl;
   const bool live = pl < cols && p < vdim;
-  const int first = cu_q[s], q_len = cu_q[s + 1] - first;
-  float* S = state + (size_t)state_slots[s] * state_stride + state_off + ((size_t)h * vdim + p) * N;
+  int first = cu_q[s], q_len = cu_q[s + 1] - first;
+  if (mode != 0) {                               // this block's slice of the request's tokens
+    if (slice * slice_len >= q_len) return;
+    first += slice * slice_len;
+    q_len = min(slice_len, q_len - slice * slice_len);
+  }
+  float* S = mode == 0 ? state + (size_t)state_slots[s] * state_stride + state_off + ((size_t)h * vdim + p) * N
+                       : slice_S + (((size_t)blockIdx.y * heads + h) * vdim + p) * N;
   float st[NPL];
 #pragma unroll
   for (int i = 0; i < NPL; ++i) {
     const int n = r + kScanLanes * i;
-    st[i] = (live && n < N) ? S[n] : 0.f;
+    st[i] = (live && n < N && mode != 1) ? S[n] : 0.f;
   }
+  float dt_sum = 0.f;
   const float neg_a = -expf(A_log[h]), bias = dt_bias[h], dskip = Dskip[h];
-  for (int c0 = 0; c0 < q_len; c0 += kScanChunk) {
-    const int nt = min(kScanChunk, q_len - c0);
+  for (int c0 = 0; c0 < q_len; c0 += chunk) {
+    const int nt = min(chunk, q_len - c0);
     __syncthreads();
     for (int idx = tid; idx < nt * N; idx += blockDim.x) {
       const int tt = idx / N, n = idx - tt * N;
@@ -118,16 +136,26 @@ __global__ void __launch_bounds__(512) ssm_scan_kernel(
       const int tt = idx / cols, pp = idx - tt * cols;
       xs[idx] = p0 + pp < vdim ? to_float(xbc[(size_t)(first + c0 + tt) * channels + h * vdim + p0 + pp]) : 0.f;
     }
-    if (tid < nt) {
-      const float dt = softplus_f(to_float(proj[(size_t)(first + c0 + tid) * proj_stride + dt_col + h]) + bias);
-      dts[tid] = dt;
-      decs[tid] = expf(neg_a * dt);
+    for (int tt = tid; tt < nt; tt += blockDim.x) {
+      const float dt = softplus_f(to_float(proj[(size_t)(first + c0 + tt) * proj_stride + dt_col + h]) + bias);
+      dts[tt] = dt;
+      decs[tt] = expf(neg_a * dt);
     }
     __syncthreads();
     {                                            // (every lane of a warp runs the loop: the shuffles want them all)
       for (int tt = 0; tt < nt; ++tt) {
         const float dec = decs[tt], xv = pl < cols ? xs[tt * cols + pl] : 0.f;
         const float dx = dts[tt] * xv;
+        dt_sum += dts[tt];
+        if (mode == 1) {                         // the state alone: nobody reads this pass's y
+          const float* Bt = Bs + tt * N;
+#pragma unroll
+          for (int i = 0; i < NPL; ++i) {
+            const int n = r + kScanLanes * i;
+            if (n < N) st[i] = fmaf(dec, st[i], dx * Bt[n]);
+          }
+          continue;
+        }
         const float* Bt = Bs + tt * N;
         const float* Ct = Cs + tt * N;
         float part = 0.f;
@@ -146,31 +174,65 @@ __global__ void __launch_bounds__(512) ssm_scan_kernel(
       }
     }
   }
-  if (live) {
+  if (live && mode != 2) {
 #pragma unroll
     for (int i = 0; i < NPL; ++i) {
       const int n = r + kScanLanes * i;
       if (n < N) S[n] = st[i];
     }
   }
+  if (mode == 1 && tid == 0 && blockIdx.z == 0) slice_a[(size_t)blockIdx.y * heads + h] = expf(neg_a * dt_sum);
+}
+
+// One thread per state value of a request: walk the request's slices in order. On entry slice_S[k] holds slice k's
+// end state from a zero start and slice_a[k] its decay; on exit slice_S[k] holds slice k's start state and the
+// request's slot its new state.
+__global__ void __launch_bounds__(256) ssm_pass_states_kernel(
+    float* __restrict__ state, long long state_stride, long long state_off, const int* __restrict__ cu_q,
+    const int* __restrict__ state_slots, float* __restrict__ slice_S, const float* __restrict__ slice_a, int heads,
+    int per_head, int slice_len, int max_slices) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int s = blockIdx.y;
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= (long long)heads * per_head) return;
+  const int h = (int)(e / per_head);
+  const int q_len = cu_q[s + 1] - cu_q[s];
+  const int n_slices = (q_len + slice_len - 1) / slice_len;
+  float* slot = state + (size_t)state_slots[s] * state_stride + state_off + e;
+  float cur = *slot;
+  for (int k = 0; k < n_slices; ++k) {
+    const size_t at = (size_t)s * max_slices + k;
+    float* p = slice_S + at * heads * per_head + e;
+    const float local = *p;
+    *p = cur;
+    cur = fmaf(slice_a[at * heads + h], cur, local);
+  }
+  *slot = cur;
 }
 
 template <typename T>
 int launch_ssm_scan(const void* xbc, int channels, const void* proj, long long proj_stride, int dt_col,
                     const float* A_log, const float* dt_bias, const float* Dskip, float* state, long long state_stride,
                     long long state_off, const int* cu_q, const int* state_slots, float* y, int n_seqs, int heads,
-                    int vdim, int N, int groups, cudaStream_t stream) {
+                    int vdim, int N, int groups, int max_q_len, int mode, int slice_len, int max_slices, float* slice_S,
+                    float* slice_a, cudaStream_t stream) {
   if (N > 32 * kScanLanes || heads % groups) return TM_ERR_UNSUPPORTED_SHAPE;
-  const int cols = vdim < 64 ? vdim : 64;
-  const int threads = ((cols * kScanLanes + 31) / 32) * 32;
-  const dim3 grid(heads, n_seqs, (vdim + cols - 1) / cols);
-  const size_t smem = (size_t)(kScanChunk * (2 * N + cols + 2)) * sizeof(float);
+  if (mode != 0 && (slice_len < 1 || max_slices < 1 || !slice_S || !slice_a)) return TM_ERR_SCRATCH_TOO_SMALL;
+  const int cols = vdim < 64 ? ((vdim + 3) / 4) * 4 : 64;          // (a multiple of 4: whole warps)
+  const int threads = cols * kScanLanes;
+  const dim3 grid(heads, mode == 0 ? n_seqs : n_seqs * max_slices, (vdim + cols - 1) / cols);
+  if (grid.y > 65535) return TM_ERR_UNSUPPORTED_SHAPE;
+  if (mode != 0) max_q_len = slice_len;
+  int chunk = max_q_len < 16 ? (max_q_len < 1 ? 1 : max_q_len) : 16;
+  while (chunk > 1 && (size_t)chunk * (2 * N + cols + 2) * sizeof(float) > 40 * 1024) chunk /= 2;
+  const size_t smem = (size_t)chunk * (2 * N + cols + 2) * sizeof(float);
   const int npl = (N + kScanLanes - 1) / kScanLanes;
 #define TM_SCAN_CASE(NPL)                                                                                            \
   if (npl <= NPL)                                                                                                    \
     return launch_pdl(ssm_scan_kernel<T, NPL>, grid, dim3(threads), smem, stream, (const T*)xbc, channels,           \
                       (const T*)proj, proj_stride, dt_col, A_log, dt_bias, Dskip, state, state_stride, state_off, cu_q, \
-                      state_slots, y, heads, vdim, N, groups, cols);
+                      state_slots, y, heads, vdim, N, groups, cols, chunk, mode, slice_len, max_slices, slice_S, slice_a);
   TM_SCAN_CASE(1) TM_SCAN_CASE(2) TM_SCAN_CASE(4) TM_SCAN_CASE(8) TM_SCAN_CASE(16) TM_SCAN_CASE(32)
 #undef TM_SCAN_CASE
   return TM_ERR_UNSUPPORTED_SHAPE;
@@ -200,19 +262,33 @@ extern "C" int tm_conv_silu_state(int dtype, const void* proj, long long proj_st
 
 // xbc [T, channels] dtype = [x (heads * vdim) | B (groups * N) | C (groups * N)] after convolution and silu; dt_raw is
 // column dt_col + h of proj; A_log, dt_bias, Dskip [heads] float; S of a request at state_off inside its slot,
-// laid out [heads, vdim, N]; y [T, heads * vdim] float.
+// laid out [heads, vdim, N]; y [T, heads * vdim] float; max_q_len: the most tokens any request brings (sizes the chunks).
+// mode 0: the whole step in order. mode 1 / 2: the first and last of the three passes over time slices (above);
+// slice_S [n_seqs * max_slices, heads, vdim, N] and slice_a [n_seqs * max_slices, heads] float.
 extern "C" int tm_ssm_scan(int dtype, const void* xbc, int channels, const void* proj, long long proj_stride, int dt_col,
                            const float* A_log, const float* dt_bias, const float* Dskip, float* state,
                            long long state_stride, long long state_off, const int* cu_q, const int* state_slots,
-                           float* y, int n_seqs, int heads, int vdim, int N, int groups, cudaStream_t stream) {
+                           float* y, int n_seqs, int heads, int vdim, int N, int groups, int max_q_len, int mode,
+                           int slice_len, int max_slices, float* slice_S, float* slice_a, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (dtype == TM_DTYPE_F32)
     return tmk::launch_ssm_scan<float>(xbc, channels, proj, proj_stride, dt_col, A_log, dt_bias, Dskip, state,
                                        state_stride, state_off, cu_q, state_slots, y, n_seqs, heads, vdim, N, groups,
-                                       stream);
+                                       max_q_len, mode, slice_len, max_slices, slice_S, slice_a, stream);
   if (dtype == TM_DTYPE_BF16)
     return tmk::launch_ssm_scan<__nv_bfloat16>(xbc, channels, proj, proj_stride, dt_col, A_log, dt_bias, Dskip, state,
                                                state_stride, state_off, cu_q, state_slots, y, n_seqs, heads, vdim, N,
-                                               groups, stream);
+                                               groups, max_q_len, mode, slice_len, max_slices, slice_S, slice_a, stream);
   return TM_ERR_BAD_DTYPE;
+}
+
+extern "C" int tm_ssm_pass_states(float* state, long long state_stride, long long state_off, const int* cu_q,
+                                  const int* state_slots, float* slice_S, const float* slice_a, int n_seqs, int heads,
+                                  int vdim, int N, int slice_len, int max_slices, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (n_seqs > 65535) return TM_ERR_UNSUPPORTED_SHAPE;
+  const long long total = (long long)heads * vdim * N;
+  return tmk::launch_pdl(tmk::ssm_pass_states_kernel, dim3((unsigned)((total + 255) / 256), n_seqs), dim3(256), 0, stream,
+                         state, state_stride, state_off, cu_q, state_slots, slice_S, slice_a, heads, vdim * N, slice_len,
+                         max_slices);
 }

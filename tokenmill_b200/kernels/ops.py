@@ -866,10 +866,12 @@ LATENT_TC_TILE_ROWS, LATENT_TILE_ROWS = 64, 32
 def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, rot_dims: int,
                      cache: torch.Tensor, block_table: torch.Tensor, cu_q: torch.Tensor, kv_before: torch.Tensor,
                      tile_seq: torch.Tensor, tile_row0: torch.Tensor, n_tiles: int, out: torch.Tensor, *, scale: float,
-                     window: int, tensor_cores: bool = False) -> torch.Tensor:
+                     window: int, tensor_cores: bool = False, n_splits: int = 1,
+                     part: torch.Tensor | None = None) -> torch.Tensor:
     """q_lat [T, nh, rank] float32, q_rot [T, nh, rot] (unrotated), out [T, nh, rank]: any strides with a unit last
     one; cache [pages, page, 1, rank + rot]. Tiles of 32 (token, head) rows, or of 64 with ``tensor_cores``
-    (bfloat16, mma.sync; see ``latent_attention_tc_ok``)."""
+    (bfloat16, mma.sync; see ``latent_attention_tc_ok``); that kernel may deal a tile's keys out in ``n_splits``
+    runs, whose partial results pass through ``part`` (n_tiles * n_splits * 64 * (rank + 2) float32)."""
     T, nh, rank = q_lat.shape
     rot = q_rot.shape[2]
     dt = cache.dtype
@@ -882,12 +884,15 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, cos: torch.Tensor
     if tensor_cores:
         if not latent_attention_tc_ok(dt, rank, rot):
             raise lib.KernelError("latent_attention: the tensor-core kernel takes bfloat16 with rank and rot multiples of 16")
+        if n_splits > 1 and (part is None or part.numel() < n_tiles * n_splits * LATENT_TC_TILE_ROWS * (rank + 2)):
+            raise lib.KernelError("latent_attention: scratch for the split runs is missing or too small")
         lib.call("tm_latent_attention_mma_bf16", q_lat.data_ptr(), q_lat.stride(0), q_lat.stride(1), q_rot.data_ptr(),
                  q_rot.stride(0), q_rot.stride(1), _req(cos, "cos", torch.float32), _req(sin, "sin", torch.float32), rot_dims,
                  _req(cache, "cache"), _req(block_table, "block_table", torch.int32), block_table.stride(0),
                  _req(cu_q, "cu_q", torch.int32), _req(kv_before, "kv_before", torch.int32),
                  _req(tile_seq, "tile_seq", torch.int32), _req(tile_row0, "tile_row0", torch.int32), n_tiles, out.data_ptr(),
-                 out.stride(0), out.stride(1), nh, rank, rot, cache.shape[1], float(scale), int(window), _stream())
+                 out.stride(0), out.stride(1), nh, rank, rot, cache.shape[1], float(scale), int(window), int(n_splits),
+                 _opt(part, "part", torch.float32), _stream())
         return out
     lib.call("tm_latent_attention", _code(dt), q_lat.data_ptr(), q_lat.stride(0), q_lat.stride(1), q_rot.data_ptr(),
              q_rot.stride(0), q_rot.stride(1), _req(cos, "cos", torch.float32), _req(sin, "sin", torch.float32), rot_dims,
@@ -912,7 +917,10 @@ def bmm_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         return out
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise lib.KernelError(f"bmm_nt: unsupported operands {a.dtype} / {w.dtype}")
-    out.copy_(torch.bmm(a, w.transpose(1, 2), out_dtype=out.dtype))
+    if out.dtype == torch.float32:
+        out.copy_(torch.bmm(a, w.transpose(1, 2), out_dtype=torch.float32))
+    else:
+        torch.bmm(a, w.transpose(1, 2), out=out)
     return out
 
 
@@ -937,18 +945,35 @@ def conv_silu_state(proj: torch.Tensor, col0: int, channels: int, weight: torch.
 
 def ssm_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, A_log: torch.Tensor, dt_bias: torch.Tensor,
              D: torch.Tensor, state: torch.Tensor, state_off: int, cu_q: torch.Tensor, state_slots: torch.Tensor,
-             y: torch.Tensor, *, n_seqs: int, heads: int, vdim: int, N: int, groups: int) -> torch.Tensor:
+             y: torch.Tensor, *, n_seqs: int, heads: int, vdim: int, N: int, groups: int, max_q_len: int = 64,
+             slice_len: int = 0, slice_S: torch.Tensor | None = None, slice_a: torch.Tensor | None = None) -> torch.Tensor:
     """The state recurrence over this step's tokens; y [T, heads * vdim] float32; S of a request lives at
-    ``state_off`` inside its slot, laid out [heads, vdim, N]."""
+    ``state_off`` inside its slot, laid out [heads, vdim, N]. ``slice_len`` > 0: three passes over time slices of
+    that many tokens (for long prompt portions), through ``slice_S`` (n_seqs * slices * heads * vdim * N float32)
+    and ``slice_a`` (n_seqs * slices * heads float32), slices = ceil(max_q_len / slice_len)."""
     T, channels = xbc.shape
     if channels != heads * vdim + 2 * groups * N or y.shape != (T, heads * vdim) or \
             state.shape[1] < state_off + heads * vdim * N or dt_col + heads > proj.shape[1]:
         raise lib.KernelError("ssm_scan: shapes do not fit")
-    lib.call("tm_ssm_scan", _code(xbc.dtype), _req(xbc, "xbc"), channels, _req(proj, "proj", xbc.dtype), proj.stride(0),
-             dt_col, _req(A_log, "A_log", torch.float32), _req(dt_bias, "dt_bias", torch.float32),
-             _req(D, "D", torch.float32), _req(state, "state", torch.float32), state.stride(0), int(state_off),
-             _req(cu_q, "cu_q", torch.int32), _req(state_slots, "state_slots", torch.int32), _req(y, "y", torch.float32),
-             int(n_seqs), heads, vdim, N, groups, _stream())
+    def scan(mode, max_slices):
+        lib.call("tm_ssm_scan", _code(xbc.dtype), _req(xbc, "xbc"), channels, _req(proj, "proj", xbc.dtype), proj.stride(0),
+                 dt_col, _req(A_log, "A_log", torch.float32), _req(dt_bias, "dt_bias", torch.float32),
+                 _req(D, "D", torch.float32), _req(state, "state", torch.float32), state.stride(0), int(state_off),
+                 _req(cu_q, "cu_q", torch.int32), _req(state_slots, "state_slots", torch.int32), _req(y, "y", torch.float32),
+                 int(n_seqs), heads, vdim, N, groups, int(max_q_len), mode, int(slice_len), max_slices,
+                 _opt(slice_S, "slice_S", torch.float32), _opt(slice_a, "slice_a", torch.float32), _stream())
+
+    if slice_len <= 0:
+        scan(0, 1)
+        return y
+    slices = -(-int(max_q_len) // int(slice_len))
+    if slice_S is None or slice_a is None or slice_S.numel() < n_seqs * slices * heads * vdim * N or \
+            slice_a.numel() < n_seqs * slices * heads:
+        raise lib.KernelError("ssm_scan: scratch for the time slices is missing or too small")
+    scan(1, slices)
+    lib.call("tm_ssm_pass_states", state.data_ptr(), state.stride(0), int(state_off), cu_q.data_ptr(), state_slots.data_ptr(),
+             slice_S.data_ptr(), slice_a.data_ptr(), int(n_seqs), heads, vdim, N, int(slice_len), slices, _stream())
+    scan(2, slices)
     return y
 
 

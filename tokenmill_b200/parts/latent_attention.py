@@ -27,6 +27,9 @@ from .base import LayerCache, StepInputs, StepMetadata, StepShape, part_limit_po
 from .spec import PagedKVNeed, PartSpec, StateNeed, WeightSpec
 
 
+SPLIT_BLOCKS = 296      # blocks the tensor-core kernel should have in flight before its keys stop being dealt out
+
+
 class LatentAttention:
     def __init__(self, *, hidden_size: int, num_heads: int, nope_dim: int, rot_dim: int, value_dim: int, q_rank: int,
                  kv_rank: int, window: int | None, scale: float, eps: float, position: PartSpec, rot_dims: int | None = None,
@@ -103,7 +106,19 @@ class LatentAttention:
         tile_seq = np.repeat(np.arange(len(per_seq), dtype=np.int32), per_seq)
         first = np.cumsum(per_seq) - per_seq
         tile_row0 = ((np.arange(tile_seq.size) - np.repeat(first, per_seq)) * self.tile_rows).astype(np.int32)
-        return StepMetadata({"tile_seq": tile_seq, "tile_row0": tile_row0}, {"n_tiles": int(tile_seq.size)},
+        # Few row tiles (decoding): deal each tile's keys out over enough blocks to put two on every multiprocessor.
+        # (A captured graph serves every context: it takes the split for the longest.)
+        n_tiles, splits = int(tile_seq.size), 1
+        if self.tensor_cores and n_tiles:
+            chunks = -(-self.rank // (64 if self.rank <= 64 else 128 if self.rank <= 128 else 256))
+            if shape.for_graph:
+                longest = shape.max_kv_len
+            else:
+                longest = int((shape.starts.astype(np.int64) + shape.q_lens).max())
+            keys = min(longest, self.window + self.tile_rows // self.nh + 1) if self.window else longest
+            key_tiles = keys // 32 + 2
+            splits = max(1, min(key_tiles // 2, SPLIT_BLOCKS // (n_tiles * chunks)))
+        return StepMetadata({"tile_seq": tile_seq, "tile_row0": tile_row0}, {"n_tiles": n_tiles, "n_splits": splits},
                             constant_in_graph=True)
 
     # --- run --------------------------------------------------------------------------------------------------
@@ -116,14 +131,21 @@ class LatentAttention:
         ops.latent_prepare(down, self.q_rank, self.rank, self.dr, self.rot_dims, self.g_q, self.g_kv, self.eps,
                            step.positions, self.cos, self.sin, slot_map, cq, cache.k)
         q = ops.linear(cq, self.w_uq).view(T, nh, self.dn + self.dr)
-        q_lat = torch.empty((nh, T, self.rank), dtype=torch.float32, device=dev)
-        ops.bmm_nt(q[:, :, :self.dn].transpose(0, 1), self.w_uk_t, q_lat)
+        if self.dtype == torch.float32:
+            q_lat = ops.bmm_nt(q[:, :, :self.dn].transpose(0, 1), self.w_uk_t,
+                               torch.empty((nh, T, self.rank), dtype=torch.float32, device=dev))
+        else:       # the library's batched product keeps its 32-bit accumulator as the result
+            q_lat = torch.bmm(q[:, :, :self.dn].transpose(0, 1), self.w_uk_t.transpose(1, 2), out_dtype=torch.float32)
         meta = step.meta[self.metadata_key()]
         o_lat = torch.empty((nh, T, self.rank), dtype=self.dtype, device=dev)
+        splits, part = meta.host["n_splits"], None
+        if splits > 1:
+            part = step.workspace.get("latent_attention_part", meta.host["n_tiles"] * splits * self.tile_rows * (self.rank + 2),
+                                      torch.float32)
         ops.latent_attention(q_lat.transpose(0, 1), q[:, :, self.dn:], self.cos, self.sin, self.rot_dims, cache.k,
                              step.block_tables[cache.group], step.cu_q, step.kv_before, meta.arrays["tile_seq"],
                              meta.arrays["tile_row0"], meta.host["n_tiles"], o_lat.transpose(0, 1), scale=self.scale,
-                             window=self.window, tensor_cores=self.tensor_cores)
+                             window=self.window, tensor_cores=self.tensor_cores, n_splits=splits, part=part)
         heads = torch.empty((T, nh, self.dv), dtype=self.dtype, device=dev)
         ops.bmm_nt(o_lat, self.w_uv, heads.transpose(0, 1))
         return ops.linear(heads.view(T, nh * self.dv), self.w_o)

@@ -21,6 +21,10 @@ from .base import LayerCache, StepInputs
 from .spec import StateNeed, WeightSpec
 
 
+SLICED_FROM = 256       # a step whose longest portion has this many tokens runs the recurrence over time slices
+SLICE_LEN = 128
+
+
 class StateSpaceMixer:
     def __init__(self, *, hidden_size: int, num_heads: int, value_dim: int, state_size: int, groups: int, conv_taps: int,
                  norm_groups: int, eps: float, names: dict[str, str] | None = None, dtype: torch.dtype,
@@ -77,9 +81,16 @@ class StateSpaceMixer:
         ops.conv_silu_state(proj, self.inner, self.channels, self.w_conv, self.b_conv, cache.state, step.cu_q,
                             step.seq_of_token, step.state_slots, xbc)
         y = torch.empty((T, self.inner), dtype=torch.float32, device=dev)
+        # Long portions: three passes over time slices instead of one walk over the whole portion (kernels/ops.py).
+        sliced = {}
+        if step.max_q_len >= SLICED_FROM and step.workspace is not None:
+            slices = -(-step.max_q_len // SLICE_LEN) * step.n_seqs
+            sliced = dict(slice_len=SLICE_LEN,
+                          slice_S=step.workspace.get("ssm_slice_states", slices * self.nh * self.dv * self.N, torch.float32),
+                          slice_a=step.workspace.get("ssm_slice_decays", slices * self.nh, torch.float32))
         ops.ssm_scan(xbc, proj, self.inner + self.channels, self.A_log, self.dt_bias, self.D, cache.state, self.conv_len,
                      step.cu_q, step.state_slots, y, n_seqs=step.n_seqs, heads=self.nh, vdim=self.dv, N=self.N,
-                     groups=self.G)
+                     groups=self.G, max_q_len=step.max_q_len, **sliced)
         gated = torch.empty((T, self.inner), dtype=self.dtype, device=dev)
         ops.gated_group_norm(y, proj, self.g, self.eps, self.norm_groups, gated)
         return ops.linear(gated, self.w_o)
