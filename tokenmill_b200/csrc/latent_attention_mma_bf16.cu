@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     const int* __restrict__ cu_q, const int* __restrict__ kv_before, const int* __restrict__ tile_seq,
     const int* __restrict__ tile_row0, __nv_bfloat16* __restrict__ out, long long out_stride_t,
     long long out_stride_h, int nh, int rank, int rot, int page_size, float scale, int window, int n_splits,
-    float* __restrict__ part) {
+    float* __restrict__ part, int stages) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int D = rank + rot;
   const int RS = D * 2 + 16;                                   // row stride in bytes: 8 rows fall into 8 different bank groups
@@ -80,30 +80,30 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
   }
   if (kt0 <= kt_last) load_keys(kt0, 0);
 
-  // Stage the queries: the latent part rounded to bfloat16, the rotated part rotated in 32-bit first.
-  for (int idx = tid; idx < kMlaRows * D; idx += 128) {
-    const int r = idx / D, d = idx - r * D;
+  // Stage the queries, a warp per row: the latent part rounded to bfloat16, the rotated part rotated in 32-bit first.
+  for (int r = warp; r < kMlaRows; r += 4) {
     const int row = row0 + r;
-    float v = 0.f;
-    if (row < n_rows) {
-      const int tok = q_start + row / nh, head = row % nh;
-      if (d < rank) {
-        v = q_lat[(size_t)tok * ql_stride_t + (size_t)head * ql_stride_h + d];
-      } else {
-        const int i = d - rank;
-        const __nv_bfloat16* qr = q_rot + (size_t)tok * qr_stride_t + (size_t)head * qr_stride_h;
-        v = to_float(qr[i]);
-        const int pos = before + row / nh;
-        if (i < half) {
-          const float c = cos_t[(size_t)pos * half + i], sn = sin_t[(size_t)pos * half + i];
-          v = __fsub_rn(__fmul_rn(v, c), __fmul_rn(to_float(qr[i + half]), sn));
-        } else if (i < rot_dims) {
-          const float c = cos_t[(size_t)pos * half + i - half], sn = sin_t[(size_t)pos * half + i - half];
-          v = __fadd_rn(__fmul_rn(v, c), __fmul_rn(to_float(qr[i - half]), sn));
-        }
-      }
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(qs + r * RS);
+    if (row >= n_rows) {
+      for (int d = lane; d < D; d += 32) dst[d] = __float2bfloat16_rn(0.f);
+      continue;
     }
-    *reinterpret_cast<__nv_bfloat16*>(qs + r * RS + d * 2) = __float2bfloat16_rn(v);
+    const int tok = q_start + row / nh, head = row % nh;
+    const float* ql = q_lat + (size_t)tok * ql_stride_t + (size_t)head * ql_stride_h;
+    for (int d = lane; d < rank; d += 32) dst[d] = __float2bfloat16_rn(ql[d]);
+    const __nv_bfloat16* qr = q_rot + (size_t)tok * qr_stride_t + (size_t)head * qr_stride_h;
+    const int pos = before + row / nh;
+    for (int i = lane; i < rot; i += 32) {
+      float v = to_float(qr[i]);
+      if (i < half) {
+        const float c = cos_t[(size_t)pos * half + i], sn = sin_t[(size_t)pos * half + i];
+        v = __fsub_rn(__fmul_rn(v, c), __fmul_rn(to_float(qr[i + half]), sn));
+      } else if (i < rot_dims) {
+        const float c = cos_t[(size_t)pos * half + i - half], sn = sin_t[(size_t)pos * half + i - half];
+        v = __fadd_rn(__fmul_rn(v, c), __fmul_rn(to_float(qr[i - half]), sn));
+      }
+      dst[rank + i] = __float2bfloat16_rn(v);
+    }
   }
 
   // The two rows of this thread inside its warp's 16: g and g + 8.
@@ -133,9 +133,12 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
   const uint32_t v_off = ((mi & 1) * 8 + lr) * RS + (mi >> 1) * 16;        // O: matrices (keys 0-7 | 8-15) x (dims 0-7 | 8-15), transposed
   const float sl2 = scale * 1.4426950408889634f;                           // scores kept in units of log2 e
 
+  // stages == 2: the next tile's copy runs under this tile's arithmetic. stages == 1 (wide rows: two blocks fit a
+  // multiprocessor only with one stage each): the copy for the next tile starts when this tile is done, and the
+  // other block's arithmetic covers it.
   int stage = 0;
-  for (int kt = kt0; kt <= kt_last; kt += kMlaKeys, stage ^= 1) {
-    if (kt + kMlaKeys <= kt_last) {
+  for (int kt = kt0; kt <= kt_last; kt += kMlaKeys, stage ^= (stages - 1)) {
+    if (stages == 2 && kt + kMlaKeys <= kt_last) {
       load_keys(kt + kMlaKeys, stage ^ 1);
       cp_async_wait<1>();
     } else {
@@ -222,6 +225,7 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
       }
     }
     __syncthreads();               // the stage is free for the load after next
+    if (stages == 1 && kt + kMlaKeys <= kt_last) load_keys(kt + kMlaKeys, 0);
   }
 
   if (n_splits > 1) {
@@ -261,39 +265,46 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
   }
 }
 
-// One block per row tile, a warp per 8 rows: merge the runs of a row in index order.
-__global__ void __launch_bounds__(256) latent_attention_combine_kernel(
+// One block per row: merge the row's runs in index order (at most 32 runs; the first warp finds their weights).
+__global__ void __launch_bounds__(128) latent_attention_combine_kernel(
     const float* __restrict__ part, int n_splits, const int* __restrict__ cu_q, const int* __restrict__ tile_seq,
     const int* __restrict__ tile_row0, __nv_bfloat16* __restrict__ out, long long out_stride_t, long long out_stride_h,
     int nh, int rank) {
+  __shared__ float wsh[33];
   pdl_launch_dependents();
   pdl_wait();
-  const int s = tile_seq[blockIdx.x], row0 = tile_row0[blockIdx.x];
+  const int tile = blockIdx.x / kMlaRows, r = blockIdx.x % kMlaRows;
+  const int s = tile_seq[tile], row0 = tile_row0[tile];
   const int q_start = cu_q[s], n_rows = (cu_q[s + 1] - q_start) * nh;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row = row0 + r;
+  if (row >= n_rows) return;
   const int W = rank + 2;
-  for (int r = warp; r < kMlaRows; r += 8) {
-    const int row = row0 + r;
-    if (row >= n_rows) break;
-    const float* base = part + ((size_t)blockIdx.x * n_splits * kMlaRows + r) * W;
-    float mx = -INFINITY;
-    for (int z = 0; z < n_splits; ++z) mx = fmaxf(mx, base[(size_t)z * kMlaRows * W + rank]);
-    float lsum = 0.f;
+  const float* base = part + ((size_t)tile * n_splits * kMlaRows + r) * W;
+  const size_t zs = (size_t)kMlaRows * W;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float mz = -INFINITY, lz = 0.f;
+    if (lane < n_splits) {
+      mz = base[lane * zs + rank];
+      lz = base[lane * zs + rank + 1];
+    }
+    const float mx = warp_max(mz);
+    const float wz = mz == -INFINITY ? 0.f : exp2f(mz - mx);
+    const float total = warp_sum(lz * wz);
+    wsh[lane] = wz;
+    if (lane == 0) wsh[32] = 1.0f / total;
+  }
+  __syncthreads();
+  const float inv = wsh[32];
+  const int tok = q_start + row / nh, head = row % nh;
+  __nv_bfloat16* dst = out + (size_t)tok * out_stride_t + (size_t)head * out_stride_h;
+  for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+    float a = 0.f;
     for (int z = 0; z < n_splits; ++z) {
-      const float* p = base + (size_t)z * kMlaRows * W;
-      if (p[rank] != -INFINITY) lsum += p[rank + 1] * exp2f(p[rank] - mx);
+      const float w = wsh[z];
+      if (w != 0.f) a = fmaf(base[z * zs + d], w, a);
     }
-    const float inv = 1.0f / lsum;
-    const int tok = q_start + row / nh, head = row % nh;
-    __nv_bfloat16* dst = out + (size_t)tok * out_stride_t + (size_t)head * out_stride_h;
-    for (int d = lane; d < rank; d += 32) {
-      float a = 0.f;
-      for (int z = 0; z < n_splits; ++z) {
-        const float* p = base + (size_t)z * kMlaRows * W;
-        if (p[rank] != -INFINITY) a = fmaf(p[d], exp2f(p[rank] - mx), a);
-      }
-      dst[d] = __float2bfloat16_rn(a * inv);
-    }
+    dst[d] = __float2bfloat16_rn(a * inv);
   }
 }
 
@@ -305,7 +316,11 @@ int launch_latent_mma(const float* q_lat, long long ql_t, long long ql_h, const 
                       int nh, int rank, int rot, int page_size, float scale, int window, int n_splits, float* part,
                       cudaStream_t stream) {
   const int D = rank + rot;
-  const size_t smem = (size_t)(kMlaRows + 2 * kMlaKeys) * (D * 2 + 16);
+  // Two stages of keys where two blocks still fit a multiprocessor with them (or one stage would not bring a second in).
+  const size_t row = (size_t)D * 2 + 16;
+  const size_t two = (kMlaRows + 2 * kMlaKeys) * row, one = (kMlaRows + kMlaKeys) * row;
+  const int stages = (two <= 113 * 1024 || one > 113 * 1024) ? 2 : 1;
+  const size_t smem = stages == 2 ? two : one;
   if (smem > 220 * 1024) return TM_ERR_UNSUPPORTED_SHAPE;
   auto kern = latent_attention_mma_kernel<NV>;
   if (smem > 48 * 1024) {
@@ -316,9 +331,9 @@ int launch_latent_mma(const float* q_lat, long long ql_t, long long ql_h, const 
   const int st = launch_pdl(kern, grid, dim3(128), smem, stream, q_lat, ql_t, ql_h, (const __nv_bfloat16*)q_rot, qr_t,
                             qr_h, cos_t, sin_t, rot_dims, (const __nv_bfloat16*)cache, block_table, bt_stride, cu_q,
                             kv_before, tile_seq, tile_row0, (__nv_bfloat16*)out, o_t, o_h, nh, rank, rot, page_size,
-                            scale, window, n_splits, part);
+                            scale, window, n_splits, part, stages);
   if (st != 0 || n_splits <= 1) return st;
-  return launch_pdl(latent_attention_combine_kernel, dim3(n_tiles), dim3(256), 0, stream, (const float*)part, n_splits,
+  return launch_pdl(latent_attention_combine_kernel, dim3(n_tiles * kMlaRows), dim3(128), 0, stream, (const float*)part, n_splits,
                     cu_q, tile_seq, tile_row0, (__nv_bfloat16*)out, o_t, o_h, nh, rank);
 }
 
@@ -334,7 +349,7 @@ extern "C" int tm_latent_attention_mma_bf16(const float* q_lat, long long ql_t, 
                                             int nh, int rank, int rot, int page_size, float scale, int window,
                                             int n_splits, float* part, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
-  if (n_splits < 1 || n_splits > 65535 || (n_splits > 1 && part == nullptr)) return TM_ERR_SCRATCH_TOO_SMALL;
+  if (n_splits < 1 || n_splits > 32 || (n_splits > 1 && part == nullptr)) return TM_ERR_SCRATCH_TOO_SMALL;
   if (rank % 16 || rot % 16 || (o_t & 1) || (o_h & 1) || (reinterpret_cast<uintptr_t>(out) & 3) ||
       (reinterpret_cast<uintptr_t>(cache) & 15))
     return TM_ERR_UNSUPPORTED_SHAPE;

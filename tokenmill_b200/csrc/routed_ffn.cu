@@ -1,10 +1,9 @@
 // Pieces of feed-forward layers beyond SwiGLU: the squared-relu activation, the router of a mixture of experts, the
 // gated activation of all experts at once with the routing weight folded in, and a batched 32-bit matrix product.
 //
-// tm_moe_route, one warp per token, all in 32-bit: logits[e] = x . W_r[e] + b[e]; the `top` largest logits are
-// chosen (lowest index first among equals); their weights are the softmax over the chosen logits alone. Outputs: the
-// chosen experts and weights ([T, top]) and a dense row of weights ([T, E], zero where not chosen). Each logit is
-// summed lane-wise over k = lane, lane + 32, ... and then across lanes, so it does not depend on the batch.
+// tm_moe_topk, one warp per token over the router's 32-bit logits (a matrix product made before it): the `top`
+// largest are chosen (lowest index first among equals); their weights are the softmax over the chosen logits alone.
+// Outputs: the chosen experts and weights ([T, top]) and a dense row of weights ([T, E], zero where not chosen).
 //
 // tm_glu_routed: gu [T, E, 2, F] (per expert: gate rows, then up rows) -> act [T, E, F] = silu(gate) * up * weight[t, e],
 // exactly zero for experts the token did not choose (their products are never looked at), so that ONE matrix product
@@ -23,11 +22,10 @@ __global__ void __launch_bounds__(256) relu2_kernel(const T* __restrict__ in, T*
   }
 }
 
-template <typename T>
-__global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w,
-                                                        const float* __restrict__ bias, int* __restrict__ top_idx,
-                                                        float* __restrict__ top_w, float* __restrict__ dense_w, int T_,
-                                                        int H, int E, int top) {
+// One warp per token over its E logits (32-bit, from a matrix product; `bias` is added here when given).
+__global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                                       int* __restrict__ top_idx, float* __restrict__ top_w,
+                                                       float* __restrict__ dense_w, int T_, int E, int top) {
   extern __shared__ float sm[];               // per warp: E logits
   pdl_launch_dependents();
   pdl_wait();
@@ -35,17 +33,12 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ x,
   const int t = blockIdx.x * (blockDim.x >> 5) + warp;
   if (t >= T_) return;
   float* logit = sm + warp * E;
-  const T* row = x + (size_t)t * H;
-  for (int e = 0; e < E; ++e) {
-    float acc = 0.f;
-    for (int k = lane; k < H; k += 32) acc = fmaf(to_float(row[k]), w[(size_t)e * H + k], acc);
-    acc = warp_sum(acc);
-    if (lane == 0) logit[e] = acc + (bias ? bias[e] : 0.f);
+  for (int e = lane; e < E; e += 32) {
+    logit[e] = logits[(size_t)t * E + e] + (bias ? bias[e] : 0.f);
+    dense_w[(size_t)t * E + e] = 0.f;
   }
   __syncwarp();
-  for (int e = lane; e < E; e += 32) dense_w[(size_t)t * E + e] = 0.f;
-  __syncwarp();
-  // `top` rounds of arg-max; a chosen logit is marked by -inf in the scratch copy and its value kept by lane 0.
+  // `top` rounds of arg-max; a chosen logit is marked by -inf in the scratch copy.
   float best0 = 0.f, denom = 0.f;
   for (int k = 0; k < top; ++k) {
     float bv = -INFINITY;
@@ -156,21 +149,14 @@ extern "C" int tm_relu2(int dtype, const void* in, void* out, long long total, c
   return TM_ERR_BAD_DTYPE;
 }
 
-// x [T, H] dtype; w [E, H], bias [E] float (bias may be null); top_idx [T, top] int; top_w [T, top], dense_w [T, E] float.
-extern "C" int tm_moe_route(int dtype, const void* x, const float* w, const float* bias, int* top_idx, float* top_w,
-                            float* dense_w, int T, int H, int E, int top, cudaStream_t stream) {
+// logits [T, E] float (bias [E] float added when given); top_idx [T, top] int; top_w [T, top], dense_w [T, E] float.
+extern "C" int tm_moe_topk(const float* logits, const float* bias, int* top_idx, float* top_w, float* dense_w, int T,
+                           int E, int top, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (top < 1 || top > E || E > 2048) return TM_ERR_UNSUPPORTED_SHAPE;
   const int warps = 4;
-  const size_t smem = (size_t)warps * E * sizeof(float);
-  const dim3 grid((T + warps - 1) / warps);
-  if (dtype == TM_DTYPE_F32)
-    return tmk::launch_pdl(tmk::moe_route_kernel<float>, grid, dim3(warps * 32), smem, stream, (const float*)x, w, bias,
-                           top_idx, top_w, dense_w, T, H, E, top);
-  if (dtype == TM_DTYPE_BF16)
-    return tmk::launch_pdl(tmk::moe_route_kernel<__nv_bfloat16>, grid, dim3(warps * 32), smem, stream,
-                           (const __nv_bfloat16*)x, w, bias, top_idx, top_w, dense_w, T, H, E, top);
-  return TM_ERR_BAD_DTYPE;
+  return tmk::launch_pdl(tmk::moe_topk_kernel, dim3((T + warps - 1) / warps), dim3(warps * 32),
+                         (size_t)warps * E * sizeof(float), stream, logits, bias, top_idx, top_w, dense_w, T, E, top);
 }
 
 // gu [T, E, 2, F], act [T, E, F] dtype; dense_w [T, E] float.

@@ -79,7 +79,7 @@ _SIGNATURES: dict[str, list] = {
     "tm_ssm_scan": [_I, _P, _I, _P, _LL, _I, _P, _P, _P, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P],
     "tm_ssm_pass_states": [_P, _LL, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "tm_relu2": [_I, _P, _P, _LL, _P],
-    "tm_moe_route": [_I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "tm_moe_topk": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
     "tm_glu_routed": [_I, _P, _P, _P, _I, _I, _I, _P],
     "tm_gemm_f32_nt_batched": [_P, _LL, _I, _P, _LL, _P, _LL, _I, _I, _I, _I, _I, _P],
     "tm_argmax": [_P, _I, _I, _LL, _P, _P, _P, _P],

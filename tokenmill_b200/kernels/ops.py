@@ -987,15 +987,25 @@ def relu2(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def moe_route(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, top: int):
-    """x [T, H]; w [E, H] float32 -> (top_idx [T, top] int32, top_w [T, top] float32, dense_w [T, E] float32)."""
+def moe_route(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, top: int, w_low: torch.Tensor | None = None):
+    """x [T, H]; w [E, H] float32 -> (top_idx [T, top] int32, top_w [T, top] float32, dense_w [T, E] float32). The
+    logits are 32-bit: this library's 32-bit product for float32 inputs; for bfloat16 inputs the library's product
+    of x with ``w_low``, a bfloat16 copy of w that holds the same values, with its 32-bit accumulator as the result
+    (products of two bfloat16 numbers are exact in 32-bit), or x converted and the 32-bit product when there is no
+    such copy."""
     T, H = x.shape
     E = w.shape[0]
+    if x.dtype == torch.float32:
+        logits, bias = linear(x, w, bias=bias), None
+    elif w_low is not None:
+        logits = torch.mm(x, w_low.t(), out_dtype=torch.float32)
+    else:
+        logits, bias = linear(x.float(), w, bias=bias), None
     idx = torch.empty((T, top), dtype=torch.int32, device=x.device)
     tw = torch.empty((T, top), dtype=torch.float32, device=x.device)
     dense = torch.empty((T, E), dtype=torch.float32, device=x.device)
-    lib.call("tm_moe_route", _code(x.dtype), _req(x, "x"), _req(w, "w", torch.float32), _opt(bias, "bias", torch.float32),
-             idx.data_ptr(), tw.data_ptr(), dense.data_ptr(), T, H, E, int(top), _stream())
+    lib.call("tm_moe_topk", _req(logits, "logits", torch.float32), _opt(bias, "bias", torch.float32), idx.data_ptr(),
+             tw.data_ptr(), dense.data_ptr(), T, E, int(top), _stream())
     return idx, tw, dense
 
 

@@ -117,7 +117,7 @@ class LatentAttention:
                 longest = int((shape.starts.astype(np.int64) + shape.q_lens).max())
             keys = min(longest, self.window + self.tile_rows // self.nh + 1) if self.window else longest
             key_tiles = keys // 32 + 2
-            splits = max(1, min(key_tiles // 2, SPLIT_BLOCKS // (n_tiles * chunks)))
+            splits = max(1, min(key_tiles // 2, SPLIT_BLOCKS // (n_tiles * chunks), 32))
         return StepMetadata({"tile_seq": tile_seq, "tile_row0": tile_row0}, {"n_tiles": n_tiles, "n_splits": splits},
                             constant_in_graph=True)
 

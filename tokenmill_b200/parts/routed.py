@@ -55,7 +55,7 @@ class RoutedExperts:
         # {e} is the expert's number
         self.names = {"router": "router", "router_bias": "router.b", "gate": "e{e}.gate", "up": "e{e}.up",
                       "down": "e{e}.down", **(names or {})}
-        self.w_router = self.b_router = self.w_gate_up = self.w_down = None
+        self.w_router = self.b_router = self.w_router_low = self.w_gate_up = self.w_down = None
 
     def weight_specs(self) -> list[WeightSpec]:
         H, F, n = self.hidden_size, self.F, self.names
@@ -75,13 +75,16 @@ class RoutedExperts:
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         n = self.names
         self.w_router, self.b_router = tensors[n["router"]], tensors[n["router_bias"]]
+        # bfloat16 runs: a bfloat16 copy of the router for the library product, if it holds the very same values
+        low = self.w_router.to(torch.bfloat16)
+        self.w_router_low = low if self.dtype == torch.bfloat16 and bool((low.float() == self.w_router).all()) else None
         self.w_gate_up = torch.cat([t for e in range(self.E) for t in (tensors[n["gate"].format(e=e)],
                                                                        tensors[n["up"].format(e=e)])], dim=0).contiguous()
         self.w_down = torch.cat([tensors[n["down"].format(e=e)] for e in range(self.E)], dim=1).contiguous()
 
     def route(self, x: torch.Tensor):
         """(chosen experts [T, top] int32, their weights [T, top] float32, dense weights [T, E] float32)."""
-        return ops.moe_route(x, self.w_router, self.b_router, self.top)
+        return ops.moe_route(x, self.w_router, self.b_router, self.top, self.w_router_low)
 
     def forward(self, x: torch.Tensor, step: StepInputs | None = None) -> torch.Tensor:
         T = x.shape[0]
