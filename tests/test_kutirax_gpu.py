@@ -224,16 +224,20 @@ def test_router_kernel(top, E):
     assert (dense.cpu().double() - ref).abs().max() < 1e-6 and int((dense != 0).sum()) == T * top
 
 
+@pytest.mark.parametrize("sizes", [dict(heads=6, vdim=7, state=11, groups=2, conv=5, norm_groups=3),
+                                   dict(heads=8, vdim=8, state=16, groups=2, conv=4, norm_groups=2)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_state_space_mixer_alone_under_cuts(dtype):
+def test_state_space_mixer_alone_under_cuts(dtype, sizes):
     """The mixer part with slots of its own: a sequence whole, and the same sequence cut 1 + 2 + 5 + 1 + rest beside
-    another request, equal the plain recurrence; sizes that are multiples of nothing."""
+    another request, equal the plain recurrence; sizes that are multiples of nothing, and sizes whose rows the
+    convolution kernel takes 16 bytes at a time."""
     from tokenmill_b200.parts.base import LayerCache, StepInputs
     from tokenmill_b200.parts.state_space import StateSpaceMixer
     torch.manual_seed(4)
     H = 40
-    mix = StateSpaceMixer(hidden_size=H, num_heads=6, value_dim=7, state_size=11, groups=2, conv_taps=5, norm_groups=3,
-                          eps=1e-5, dtype=dtype, device=torch.device(DEV))
+    p = sizes
+    mix = StateSpaceMixer(hidden_size=H, num_heads=p["heads"], value_dim=p["vdim"], state_size=p["state"], groups=p["groups"],
+                          conv_taps=p["conv"], norm_groups=p["norm_groups"], eps=1e-5, dtype=dtype, device=torch.device(DEV))
     tensors, plain_w = {}, {}
     for s in mix.weight_specs():
         t = torch.randn(s.shape) * (0.3 if len(s.shape) > 1 else 0.5)
@@ -243,7 +247,6 @@ def test_state_space_mixer_alone_under_cuts(dtype):
         plain_w[s.name] = t.double()
         tensors[s.name] = t.to(DEV, dtype if s.dtype == "compute" else torch.float32)
     mix.bind(tensors)
-    p = dict(heads=6, vdim=7, state=11, groups=2, conv=5, norm_groups=3)
     seqs = [torch.randn(23, H).to(torch.bfloat16).float(), torch.randn(9, H).to(torch.bfloat16).float()]
     want = [pk.mamba2(s.double(), plain_w, p, 1e-5) for s in seqs]
     state = torch.zeros(4, mix.state_need().shape[0], device=DEV)

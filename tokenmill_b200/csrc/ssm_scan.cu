@@ -79,6 +79,87 @@ __global__ void __launch_bounds__(256) conv_silu_state_kernel(
   }
 }
 
+// The same with VEC consecutive channels per thread (16 bytes per access) for the rows that need no carried input;
+// a request's first row still owns the slot and walks its VEC channels one after the other.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(128) conv_silu_state_vec_kernel(
+    const T* __restrict__ proj, long long proj_stride, int col0, int channels, int taps,
+    const float* __restrict__ weight, const float* __restrict__ bias, float* __restrict__ state,
+    long long state_stride, const int* __restrict__ cu_q, const int* __restrict__ seq_of_token,
+    const int* __restrict__ state_slots, T* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+  if (c0 >= channels) return;
+  const int s = seq_of_token[t];
+  const int first = cu_q[s];
+  const int j = t - first;
+  const int carried = taps - 1;
+  if (j > 0 && j < carried) return;
+  if (j >= carried) {
+    float acc[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+    for (int k = 0; k < taps; ++k) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(proj + (size_t)(t - carried + k) * proj_stride + col0 + c0);
+      const T* v = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] = fmaf(weight[(size_t)(c0 + e) * taps + k], to_float(v[e]), acc[e]);
+    }
+    uint4 res;
+    T* o = reinterpret_cast<T*>(&res);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      const float a = acc[e] + (bias ? bias[c0 + e] : 0.f);
+      o[e] = from_float<T>(a / (1.0f + expf(-a)));
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)t * channels + c0) = res;
+    return;
+  }
+  const int q_len = cu_q[s + 1] - first;
+  for (int e = 0; e < VEC; ++e) {
+    const int c = c0 + e;
+    float w[kMaxTaps], old[kMaxTaps];
+    for (int k = 0; k < taps; ++k) w[k] = weight[(size_t)c * taps + k];
+    const float bv = bias ? bias[c] : 0.f;
+    const T* in = proj + col0 + c;
+    float* slot = state + (size_t)state_slots[s] * state_stride + c;
+    for (int i = 0; i < carried; ++i) old[i] = slot[(size_t)i * channels];
+    const int n_head = min(carried, q_len);
+    for (int jj = 0; jj < n_head; ++jj) {
+      float acc = 0.f;
+      for (int k = 0; k < taps; ++k) {
+        const int src = jj - carried + k;
+        const float v = src >= 0 ? to_float(in[(size_t)(first + src) * proj_stride]) : old[carried + src];
+        acc = fmaf(w[k], v, acc);
+      }
+      acc += bv;
+      out[(size_t)(first + jj) * channels + c] = from_float<T>(acc / (1.0f + expf(-acc)));
+    }
+    for (int i = 0; i < carried; ++i) {
+      const int src = q_len - carried + i;
+      slot[(size_t)i * channels] = src >= 0 ? to_float(in[(size_t)(first + src) * proj_stride]) : old[i + q_len];
+    }
+  }
+}
+
+template <typename T>
+int launch_conv_silu_state(const void* proj, long long proj_stride, int col0, int channels, int taps, const float* weight,
+                           const float* bias, float* state, long long state_stride, const int* cu_q,
+                           const int* seq_of_token, const int* state_slots, void* out, int T_, cudaStream_t stream) {
+  constexpr int VEC = 16 / sizeof(T);
+  const bool aligned = channels % VEC == 0 && col0 % VEC == 0 && proj_stride % VEC == 0 &&
+                       ((reinterpret_cast<uintptr_t>(proj) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  if (aligned)
+    return launch_pdl(conv_silu_state_vec_kernel<T, VEC>, dim3(T_, (channels / VEC + 127) / 128), dim3(128), 0, stream,
+                      (const T*)proj, proj_stride, col0, channels, taps, weight, bias, state, state_stride, cu_q,
+                      seq_of_token, state_slots, (T*)out);
+  return launch_pdl(conv_silu_state_kernel<T>, dim3(T_, (channels + 255) / 256), dim3(256), 0, stream, (const T*)proj,
+                    proj_stride, col0, channels, taps, weight, bias, state, state_stride, cu_q, seq_of_token, state_slots,
+                    (T*)out);
+}
+
 constexpr int kScanLanes = 8;        // lanes that share one column of the state
 
 __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
@@ -248,15 +329,12 @@ extern "C" int tm_conv_silu_state(int dtype, const void* proj, long long proj_st
                                   cudaStream_t stream) {
   if (T <= 0) return 0;
   if (taps < 1 || taps > tmk::kMaxTaps) return TM_ERR_UNSUPPORTED_SHAPE;
-  const dim3 grid(T, (channels + 255) / 256);
   if (dtype == TM_DTYPE_F32)
-    return tmk::launch_pdl(tmk::conv_silu_state_kernel<float>, grid, dim3(256), 0, stream, (const float*)proj,
-                           proj_stride, col0, channels, taps, weight, bias, state, state_stride, cu_q, seq_of_token,
-                           state_slots, (float*)out);
+    return tmk::launch_conv_silu_state<float>(proj, proj_stride, col0, channels, taps, weight, bias, state, state_stride,
+                                              cu_q, seq_of_token, state_slots, out, T, stream);
   if (dtype == TM_DTYPE_BF16)
-    return tmk::launch_pdl(tmk::conv_silu_state_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream,
-                           (const __nv_bfloat16*)proj, proj_stride, col0, channels, taps, weight, bias, state,
-                           state_stride, cu_q, seq_of_token, state_slots, (__nv_bfloat16*)out);
+    return tmk::launch_conv_silu_state<__nv_bfloat16>(proj, proj_stride, col0, channels, taps, weight, bias, state,
+                                                      state_stride, cu_q, seq_of_token, state_slots, out, T, stream);
   return TM_ERR_BAD_DTYPE;
 }
 
