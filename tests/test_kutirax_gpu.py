@@ -151,7 +151,7 @@ def test_pair_norm_and_token_shift_kernels(dtype):
 
 
 @pytest.mark.parametrize("nh,rank,rot,rot_dims,window,page", [(5, 48, 16, 16, 33, 16), (16, 64, 32, 16, 7, 8), (3, 160, 16, 16, 400, 16),
-                                                             (7, 72, 6, 4, 20, 16), (4, 272, 32, 32, 1, 32)])
+                                                             (7, 72, 6, 4, 20, 16), (4, 272, 32, 32, 1, 32), (40, 32, 16, 16, 50, 16)])
 def test_latent_attention_kernels(nh, rank, rot, rot_dims, window, page):
     """The attention kernels alone over a hand-made paged cache of latents: three requests (a prompt portion that
     continues 150 cached tokens, a single decoded token at position 400, a fresh prompt) against a plain 64-bit
@@ -225,7 +225,8 @@ def test_router_kernel(top, E):
 
 
 @pytest.mark.parametrize("sizes", [dict(heads=6, vdim=7, state=11, groups=2, conv=5, norm_groups=3),
-                                   dict(heads=8, vdim=8, state=16, groups=2, conv=4, norm_groups=2)])
+                                   dict(heads=8, vdim=8, state=16, groups=2, conv=4, norm_groups=2),
+                                   dict(heads=2, vdim=70, state=1, groups=1, conv=1, norm_groups=1)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_state_space_mixer_alone_under_cuts(dtype, sizes):
     """The mixer part with slots of its own: a sequence whole, and the same sequence cut 1 + 2 + 5 + 1 + rest beside
@@ -291,6 +292,34 @@ def test_replay_matches_plain(kutirax_dirs, size, dtype, mode, tmp_path, plain_c
     outputs = run_trace(folder, dtype, steps, max_tokens, tmp_path / "out")
     frac = _check(steps, outputs, reqs, _plain(folder, reqs, plain_cache), dtype)
     print(f"{size} {dtype} {mode}: {frac}")
+
+
+@pytest.mark.parametrize("order", ["state_space_only", "attention_only", "three_windows", "one_layer"])
+def test_other_layer_orders(order, tmp_path):
+    """Models without any paged cache (state-space layers only), without any mixer state (attention only; the shift's
+    state remains), with three windows (three cache groups, one of them longer than any request), and of one layer."""
+    from tokenmill_b200.weights import write_random_model
+    from tokenmill_b200.weights.random_init import kutirax_config, kutirax_latent, kutirax_mamba
+    L, M = "latent_attention", "mamba2"
+    lat = lambda w, **kw: kutirax_latent(heads=4, dim=8, rot_dim=8, vdim=6, q_rank=12, kv_rank=16, window=w, **kw)     # noqa: E731
+    layers = {
+        "state_space_only": [(M, kutirax_mamba(heads=4, vdim=8, state=8, groups=2, conv=3, norm_groups=2), ("dense", 48)),
+                             (M, kutirax_mamba(heads=2, vdim=12, state=6, groups=2, conv=2), None)],
+        "attention_only": [(L, lat(11), ("moe", 6, 2, 16)), (L, lat(11), None), (L, lat(11), ("dense", 40))],
+        "three_windows": [(L, lat(5), None), (L, lat(1000), ("dense", 32)), (L, lat(64), None)],
+        "one_layer": [(L, lat(17, rot_dims=4), ("moe", 2, 1, 8))],
+    }[order]
+    cfg = kutirax_config(vocab=97, width=40, eps=1e-5, residual_mult=0.8, layers=layers)
+    folder = write_random_model(tmp_path / "m", cfg, seed=8)
+    reqs = make_requests(97, [70, 133, 45, 96], seed=15)
+    _, w = _read(folder)
+    plain = {r: pk.forward(cfg, w, t).float() for r, t in reqs.items()}
+    for mode in ("whole", "mixed"):
+        steps, max_tokens = _steps(mode, reqs)
+        outputs = run_trace(folder, "float32", steps, max_tokens, tmp_path / mode)
+        check_against_plain(steps, outputs, reqs, plain, "float32")
+    steps, max_tokens = _steps("mixed", reqs)
+    _check(steps, run_trace(folder, "bfloat16", steps, max_tokens, tmp_path / "bf16"), reqs, plain, "bfloat16")
 
 
 @pytest.mark.parametrize("page", [8, 32])

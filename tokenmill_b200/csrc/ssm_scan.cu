@@ -79,9 +79,9 @@ __global__ void __launch_bounds__(256) conv_silu_state_kernel(
   }
 }
 
-// The same with VEC consecutive channels per thread (16 bytes per access) for the rows that need no carried input;
+// The same with VEC consecutive channels per thread (16 bytes per access; 2 to 4 taps) for the rows that need no carried input;
 // a request's first row still owns the slot and walks its VEC channels one after the other.
-template <typename T, int VEC>
+template <typename T, int VEC, int TAPS>
 __global__ void __launch_bounds__(128) conv_silu_state_vec_kernel(
     const T* __restrict__ proj, long long proj_stride, int col0, int channels, int taps,
     const float* __restrict__ weight, const float* __restrict__ bias, float* __restrict__ state,
@@ -98,14 +98,20 @@ __global__ void __launch_bounds__(128) conv_silu_state_vec_kernel(
   const int carried = taps - 1;
   if (j > 0 && j < carried) return;
   if (j >= carried) {
-    float acc[VEC];
+    float acc[VEC], wr[VEC * TAPS];          // the thread's VEC x TAPS weights lie side by side: 16 bytes per load
+#pragma unroll
+    for (int i = 0; i < VEC * TAPS / 4; ++i) {
+      const float4 w4 = *reinterpret_cast<const float4*>(weight + (size_t)c0 * TAPS + 4 * i);
+      wr[4 * i] = w4.x; wr[4 * i + 1] = w4.y; wr[4 * i + 2] = w4.z; wr[4 * i + 3] = w4.w;
+    }
 #pragma unroll
     for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
-    for (int k = 0; k < taps; ++k) {
+#pragma unroll
+    for (int k = 0; k < TAPS; ++k) {
       const uint4 raw = *reinterpret_cast<const uint4*>(proj + (size_t)(t - carried + k) * proj_stride + col0 + c0);
       const T* v = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) acc[e] = fmaf(weight[(size_t)(c0 + e) * taps + k], to_float(v[e]), acc[e]);
+      for (int e = 0; e < VEC; ++e) acc[e] = fmaf(wr[e * TAPS + k], to_float(v[e]), acc[e]);
     }
     uint4 res;
     T* o = reinterpret_cast<T*>(&res);
@@ -150,11 +156,15 @@ int launch_conv_silu_state(const void* proj, long long proj_stride, int col0, in
                            const int* seq_of_token, const int* state_slots, void* out, int T_, cudaStream_t stream) {
   constexpr int VEC = 16 / sizeof(T);
   const bool aligned = channels % VEC == 0 && col0 % VEC == 0 && proj_stride % VEC == 0 &&
-                       ((reinterpret_cast<uintptr_t>(proj) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
-  if (aligned)
-    return launch_pdl(conv_silu_state_vec_kernel<T, VEC>, dim3(T_, (channels / VEC + 127) / 128), dim3(128), 0, stream,
-                      (const T*)proj, proj_stride, col0, channels, taps, weight, bias, state, state_stride, cu_q,
-                      seq_of_token, state_slots, (T*)out);
+                       ((reinterpret_cast<uintptr_t>(proj) | reinterpret_cast<uintptr_t>(out) |
+                         reinterpret_cast<uintptr_t>(weight)) & 15) == 0;
+#define TM_CONV_VEC(TAPS)                                                                                            \
+  if (aligned && taps == TAPS)                                                                                       \
+    return launch_pdl(conv_silu_state_vec_kernel<T, VEC, TAPS>, dim3(T_, (channels / VEC + 127) / 128), dim3(128), 0,  \
+                      stream, (const T*)proj, proj_stride, col0, channels, taps, weight, bias, state, state_stride,  \
+                      cu_q, seq_of_token, state_slots, (T*)out);
+  TM_CONV_VEC(2) TM_CONV_VEC(3) TM_CONV_VEC(4)
+#undef TM_CONV_VEC
   return launch_pdl(conv_silu_state_kernel<T>, dim3(T_, (channels + 255) / 256), dim3(256), 0, stream, (const T*)proj,
                     proj_stride, col0, channels, taps, weight, bias, state, state_stride, cu_q, seq_of_token, state_slots,
                     (T*)out);
