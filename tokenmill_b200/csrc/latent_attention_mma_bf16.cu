@@ -57,15 +57,15 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
   const int half = rot_dims >> 1;
   const int segs = D / 8;                                      // 16-byte pieces of a cache row
 
+  // A warp per key row (8 rows a warp): one page lookup per row, lanes over the row's 16-byte pieces.
   auto load_keys = [&](int kt, int stage) {
     unsigned char* dst = ks + stage * (kMlaKeys * RS);
-    for (int idx = tid; idx < kMlaKeys * segs; idx += 128) {
-      const int jj = idx / segs, sg = idx - jj * segs;
+    for (int jj = warp; jj < kMlaKeys; jj += 4) {
       const int j = kt + jj;
       const bool ok = j >= j_lo && j <= j_hi;
       const __nv_bfloat16* src = cache;
-      if (ok) src = cache + ((size_t)table[j / page_size] * page_size + (j % page_size)) * D + sg * 8;
-      cp_async16(smem_u32(dst + jj * RS + sg * 16), src, ok);
+      if (ok) src = cache + ((size_t)table[j / page_size] * page_size + (j % page_size)) * D;
+      for (int sg = lane; sg < segs; sg += 32) cp_async16(smem_u32(dst + jj * RS + sg * 16), ok ? src + sg * 8 : src, ok);
     }
     cp_async_commit();
   };
@@ -152,6 +152,7 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     for (int n = 0; n < 4; ++n)
 #pragma unroll
       for (int e = 0; e < 4; ++e) sc[n][e] = 0.f;
+#pragma unroll 3
     for (int kk = 0; kk < D; kk += 16) {
       uint32_t a[4], b0, b1, b2, b3;
       ldmatrix_x4(q_base + kk * 2, a[0], a[1], a[2], a[3]);

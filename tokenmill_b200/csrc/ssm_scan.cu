@@ -12,8 +12,8 @@
 // tm_ssm_scan: per head h (group g = h / (heads / groups)) and token t, all in 32-bit:
 //   dt = softplus(dt_raw + dt_bias[h])        a = exp(-exp(A_log[h]) * dt)
 //   S <- a * S + dt * B_t x_t^T               y_t = S^T C_t + D[h] * x_t
-// One block per (head, request, slice of vdim); each of a block's columns p is served by 8 lanes that hold N / 8
-// state values each in registers for the whole step. Tokens are taken in chunks through shared memory and
+// One block per (head, request, slice of vdim); each group of 4 columns p is served by 8 lanes that hold N / 8
+// state values of each of them in registers for the whole step (one load of B and of C serves the four). Tokens are taken in chunks through shared memory and
 // walked strictly in order, so the result does not depend on how a request was cut into steps.
 //
 // A long prompt portion would leave one block per (head, request) walking thousands of tokens one after the other
@@ -174,13 +174,16 @@ constexpr int kScanLanes = 8;        // lanes that share one column of the state
 
 __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 
-template <typename T, int NPL>       // NPL = ceil(N / 8) state values per lane
-__global__ void __launch_bounds__(512) ssm_scan_kernel(
+constexpr int kScanCols = 4;         // columns of the state a thread holds: they share every load of B and C
+
+template <typename T, int NPL>       // NPL = ceil(N / 8) state values per lane and column
+__global__ void __launch_bounds__(128) ssm_scan_kernel(
     const T* __restrict__ xbc, int channels, const T* __restrict__ proj, long long proj_stride, int dt_col,
     const float* __restrict__ A_log, const float* __restrict__ dt_bias, const float* __restrict__ Dskip,
     float* __restrict__ state, long long state_stride, long long state_off, const int* __restrict__ cu_q,
     const int* __restrict__ state_slots, float* __restrict__ y, int heads, int vdim, int N, int groups, int cols,
-    int chunk, int mode, int slice_len, int max_slices, float* __restrict__ slice_S, float* __restrict__ slice_a) {
+    int chunk, int mode, int slice_len, int max_slices, float* __restrict__ slice_S, float* __restrict__ slice_a,
+    int vec) {
   extern __shared__ __align__(16) float sm[];
   float* Bs = sm;                               // [chunk][N]
   float* Cs = Bs + chunk * N;                   // [chunk][N]
@@ -195,37 +198,63 @@ __global__ void __launch_bounds__(512) ssm_scan_kernel(
   const int g = h / (heads / groups);
   const int inner = heads * vdim;
   const int tid = threadIdx.x;
-  const int r = tid & (kScanLanes - 1), pl = tid / kScanLanes;
-  const int p = p0 + pl;
-  const bool live = pl < cols && p < vdim;
+  const int r = tid & (kScanLanes - 1), pl = (tid / kScanLanes) * kScanCols;      // first of the thread's columns
   int first = cu_q[s], q_len = cu_q[s + 1] - first;
   if (mode != 0) {                               // this block's slice of the request's tokens
     if (slice * slice_len >= q_len) return;
     first += slice * slice_len;
     q_len = min(slice_len, q_len - slice * slice_len);
   }
-  float* S = mode == 0 ? state + (size_t)state_slots[s] * state_stride + state_off + ((size_t)h * vdim + p) * N
-                       : slice_S + (((size_t)blockIdx.y * heads + h) * vdim + p) * N;
-  float st[NPL];
+  float* Sbase = mode == 0 ? state + (size_t)state_slots[s] * state_stride + state_off + (size_t)h * vdim * N
+                           : slice_S + ((size_t)blockIdx.y * heads + h) * vdim * N;
+  bool live[kScanCols];
+  float st[kScanCols][NPL];
 #pragma unroll
-  for (int i = 0; i < NPL; ++i) {
-    const int n = r + kScanLanes * i;
-    st[i] = (live && n < N && mode != 1) ? S[n] : 0.f;
+  for (int q = 0; q < kScanCols; ++q) {
+    const int p = p0 + pl + q;
+    live[q] = pl + q < cols && p < vdim;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int n = r + kScanLanes * i;
+      st[q][i] = (live[q] && n < N && mode != 1) ? Sbase[(size_t)p * N + n] : 0.f;
+    }
   }
   float dt_sum = 0.f;
   const float neg_a = -expf(A_log[h]), bias = dt_bias[h], dskip = Dskip[h];
   for (int c0 = 0; c0 < q_len; c0 += chunk) {
     const int nt = min(chunk, q_len - c0);
     __syncthreads();
-    for (int idx = tid; idx < nt * N; idx += blockDim.x) {
-      const int tt = idx / N, n = idx - tt * N;
-      const T* row = xbc + (size_t)(first + c0 + tt) * channels + inner + g * N + n;
-      Bs[idx] = to_float(row[0]);
-      Cs[idx] = to_float(row[groups * N]);
-    }
-    for (int idx = tid; idx < nt * cols; idx += blockDim.x) {
-      const int tt = idx / cols, pp = idx - tt * cols;
-      xs[idx] = p0 + pp < vdim ? to_float(xbc[(size_t)(first + c0 + tt) * channels + h * vdim + p0 + pp]) : 0.f;
+    if (vec) {                                   // rows of B, C and x in 16-byte pieces (the host checked the alignment)
+      constexpr int VEC = 16 / sizeof(T);
+      const int per_row = N / VEC, per_x = cols / VEC;
+      for (int idx = tid; idx < 2 * nt * per_row; idx += blockDim.x) {
+        const int which = idx / (nt * per_row), rem = idx - which * nt * per_row;
+        const int tt = rem / per_row, v = rem - tt * per_row;
+        const uint4 raw = *reinterpret_cast<const uint4*>(xbc + (size_t)(first + c0 + tt) * channels + inner + g * N +
+                                                          which * groups * N + v * VEC);
+        const T* e = reinterpret_cast<const T*>(&raw);
+        float* dst = (which ? Cs : Bs) + tt * N + v * VEC;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) dst[k] = to_float(e[k]);
+      }
+      for (int idx = tid; idx < nt * per_x; idx += blockDim.x) {
+        const int tt = idx / per_x, v = idx - tt * per_x;
+        const uint4 raw = *reinterpret_cast<const uint4*>(xbc + (size_t)(first + c0 + tt) * channels + h * vdim + p0 + v * VEC);
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) xs[tt * cols + v * VEC + k] = to_float(e[k]);
+      }
+    } else {
+      for (int idx = tid; idx < nt * N; idx += blockDim.x) {
+        const int tt = idx / N, n = idx - tt * N;
+        const T* row = xbc + (size_t)(first + c0 + tt) * channels + inner + g * N + n;
+        Bs[idx] = to_float(row[0]);
+        Cs[idx] = to_float(row[groups * N]);
+      }
+      for (int idx = tid; idx < nt * cols; idx += blockDim.x) {
+        const int tt = idx / cols, pp = idx - tt * cols;
+        xs[idx] = p0 + pp < vdim ? to_float(xbc[(size_t)(first + c0 + tt) * channels + h * vdim + p0 + pp]) : 0.f;
+      }
     }
     for (int tt = tid; tt < nt; tt += blockDim.x) {
       const float dt = softplus_f(to_float(proj[(size_t)(first + c0 + tt) * proj_stride + dt_col + h]) + bias);
@@ -233,43 +262,61 @@ __global__ void __launch_bounds__(512) ssm_scan_kernel(
       decs[tt] = expf(neg_a * dt);
     }
     __syncthreads();
-    {                                            // (every lane of a warp runs the loop: the shuffles want them all)
-      for (int tt = 0; tt < nt; ++tt) {
-        const float dec = decs[tt], xv = pl < cols ? xs[tt * cols + pl] : 0.f;
-        const float dx = dts[tt] * xv;
-        dt_sum += dts[tt];
-        if (mode == 1) {                         // the state alone: nobody reads this pass's y
-          const float* Bt = Bs + tt * N;
+    for (int tt = 0; tt < nt; ++tt) {            // (every lane of a warp runs the loop: the shuffles want them all)
+      const float dec = decs[tt], dt = dts[tt];
+      const float* Bt = Bs + tt * N;
+      const float* Ct = Cs + tt * N;
+      float xv[kScanCols], dx[kScanCols], part[kScanCols];
 #pragma unroll
-          for (int i = 0; i < NPL; ++i) {
-            const int n = r + kScanLanes * i;
-            if (n < N) st[i] = fmaf(dec, st[i], dx * Bt[n]);
-          }
-          continue;
-        }
-        const float* Bt = Bs + tt * N;
-        const float* Ct = Cs + tt * N;
-        float part = 0.f;
+      for (int q = 0; q < kScanCols; ++q) {
+        xv[q] = pl + q < cols ? xs[tt * cols + pl + q] : 0.f;
+        dx[q] = dt * xv[q];
+        part[q] = 0.f;
+      }
+      dt_sum += dt;
+      if (mode == 1) {                           // the state alone: nobody reads this pass's y
 #pragma unroll
         for (int i = 0; i < NPL; ++i) {
           const int n = r + kScanLanes * i;
           if (n < N) {
-            st[i] = fmaf(dec, st[i], dx * Bt[n]);
-            part = fmaf(st[i], Ct[n], part);
+            const float bv = Bt[n];
+#pragma unroll
+            for (int q = 0; q < kScanCols; ++q) st[q][i] = fmaf(dec, st[q][i], dx[q] * bv);
           }
         }
-        part += __shfl_xor_sync(0xffffffffu, part, 1);
-        part += __shfl_xor_sync(0xffffffffu, part, 2);
-        part += __shfl_xor_sync(0xffffffffu, part, 4);
-        if (r == 0 && live) y[(size_t)(first + c0 + tt) * inner + h * vdim + p] = fmaf(dskip, xv, part);
+        continue;
+      }
+#pragma unroll
+      for (int i = 0; i < NPL; ++i) {
+        const int n = r + kScanLanes * i;
+        if (n < N) {
+          const float bv = Bt[n], cv = Ct[n];
+#pragma unroll
+          for (int q = 0; q < kScanCols; ++q) {
+            st[q][i] = fmaf(dec, st[q][i], dx[q] * bv);
+            part[q] = fmaf(st[q][i], cv, part[q]);
+          }
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < kScanCols; ++q) {
+        part[q] += __shfl_xor_sync(0xffffffffu, part[q], 1);
+        part[q] += __shfl_xor_sync(0xffffffffu, part[q], 2);
+        part[q] += __shfl_xor_sync(0xffffffffu, part[q], 4);
+        if (r == 0 && live[q])
+          y[(size_t)(first + c0 + tt) * inner + h * vdim + p0 + pl + q] = fmaf(dskip, xv[q], part[q]);
       }
     }
   }
-  if (live && mode != 2) {
+  if (mode != 2) {
 #pragma unroll
-    for (int i = 0; i < NPL; ++i) {
-      const int n = r + kScanLanes * i;
-      if (n < N) S[n] = st[i];
+    for (int q = 0; q < kScanCols; ++q) {
+      if (!live[q]) continue;
+#pragma unroll
+      for (int i = 0; i < NPL; ++i) {
+        const int n = r + kScanLanes * i;
+        if (n < N) Sbase[(size_t)(p0 + pl + q) * N + n] = st[q][i];
+      }
     }
   }
   if (mode == 1 && tid == 0 && blockIdx.z == 0) slice_a[(size_t)blockIdx.y * heads + h] = expf(neg_a * dt_sum);
@@ -311,19 +358,22 @@ int launch_ssm_scan(const void* xbc, int channels, const void* proj, long long p
   if (N > 32 * kScanLanes || heads % groups) return TM_ERR_UNSUPPORTED_SHAPE;
   if (mode != 0 && (slice_len < 1 || max_slices < 1 || !slice_S || !slice_a)) return TM_ERR_SCRATCH_TOO_SMALL;
   const int cols = vdim < 64 ? ((vdim + 3) / 4) * 4 : 64;          // (a multiple of 4: whole warps)
-  const int threads = cols * kScanLanes;
+  const int threads = ((cols / kScanCols * kScanLanes + 31) / 32) * 32;
   const dim3 grid(heads, mode == 0 ? n_seqs : n_seqs * max_slices, (vdim + cols - 1) / cols);
   if (grid.y > 65535) return TM_ERR_UNSUPPORTED_SHAPE;
   if (mode != 0) max_q_len = slice_len;
   int chunk = max_q_len < 16 ? (max_q_len < 1 ? 1 : max_q_len) : 16;
   while (chunk > 1 && (size_t)chunk * (2 * N + cols + 2) * sizeof(float) > 40 * 1024) chunk /= 2;
   const size_t smem = (size_t)chunk * (2 * N + cols + 2) * sizeof(float);
+  constexpr int VEC = 16 / sizeof(T);
+  const int vec = N % VEC == 0 && channels % VEC == 0 && vdim % VEC == 0 && cols % VEC == 0 && vdim % cols == 0 &&
+                  (reinterpret_cast<uintptr_t>(xbc) & 15) == 0;
   const int npl = (N + kScanLanes - 1) / kScanLanes;
 #define TM_SCAN_CASE(NPL)                                                                                            \
   if (npl <= NPL)                                                                                                    \
     return launch_pdl(ssm_scan_kernel<T, NPL>, grid, dim3(threads), smem, stream, (const T*)xbc, channels,           \
                       (const T*)proj, proj_stride, dt_col, A_log, dt_bias, Dskip, state, state_stride, state_off, cu_q, \
-                      state_slots, y, heads, vdim, N, groups, cols, chunk, mode, slice_len, max_slices, slice_S, slice_a);
+                      state_slots, y, heads, vdim, N, groups, cols, chunk, mode, slice_len, max_slices, slice_S, slice_a, vec);
   TM_SCAN_CASE(1) TM_SCAN_CASE(2) TM_SCAN_CASE(4) TM_SCAN_CASE(8) TM_SCAN_CASE(16) TM_SCAN_CASE(32)
 #undef TM_SCAN_CASE
   return TM_ERR_UNSUPPORTED_SHAPE;
