@@ -192,10 +192,10 @@ def test_latent_attention_kernels(nh, rank, rot, rot_dims, window, page):
     t32 = lambda a: torch.as_tensor(np.asarray(a, dtype=np.int32), device=DEV)      # noqa: E731
     cu = np.zeros(4, dtype=np.int32)
     cu[1:] = np.cumsum(lens)
-    kinds = [(False, 32, 1)] + ([(True, 64, 1), (True, 64, 3), (True, 64, 32)]
-                                if ops.latent_attention_tc_ok(torch.bfloat16, rank, rot) else [])
-    assert len(kinds) == 4 or rank % 16 or rot % 16
-    for tc, tile, splits in kinds:
+    kinds = [(False, 32, 1, False)] + ([(True, 64, 1, False), (True, 64, 3, False), (True, 64, 32, False), (True, 64, 1, True),
+                                        (True, 64, 5, True)] if ops.latent_attention_tc_ok(torch.bfloat16, rank, rot) else [])
+    assert len(kinds) == 6 or rank % 16 or rot % 16
+    for tc, tile, splits, paired in kinds:
         per = [-(-n * nh // tile) for n in lens]
         tile_seq = np.repeat(np.arange(3), per)
         tile_row0 = np.concatenate([np.arange(k) * tile for k in per])
@@ -203,10 +203,10 @@ def test_latent_attention_kernels(nh, rank, rot, rot_dims, window, page):
         part = torch.full((len(tile_seq) * splits * 64 * (rank + 2),), float("nan"), device=DEV) if splits > 1 else None
         ops.latent_attention(q_lat.to(DEV), q_rot.to(DEV), cos.to(DEV), sin.to(DEV), rot_dims, cache.to(DEV), t32(table),
                              t32(cu), t32(starts), t32(tile_seq), t32(tile_row0), len(tile_seq), out.transpose(0, 1),
-                             scale=scale, window=window, tensor_cores=tc, n_splits=splits, part=part)
+                             scale=scale, window=window, tensor_cores=tc, n_splits=splits, part=part, paired=paired)
         got = out.transpose(0, 1).float().cpu().double()
         err = float((got - ref).abs().max())
-        assert err < 2e-2, (tc, splits, err)
+        assert err < 2e-2, (tc, splits, paired, err)
 
 
 @pytest.mark.parametrize("top,E", [(1, 5), (3, 12), (4, 4), (2, 37)])

@@ -861,13 +861,21 @@ def latent_attention_tc_ok(dtype: torch.dtype, rank: int, rot: int) -> bool:
 
 
 LATENT_TC_TILE_ROWS, LATENT_TILE_ROWS = 64, 32
+LATENT_TC_PAIRED = os.environ.get("TOKENMILL_LATENT_PAIRED", "1") != "0"    # the tensor-core kernel with warps in pairs
+
+
+def latent_attention_tc_chunks(rank: int) -> int:
+    """Blocks that share a row tile of the tensor-core kernel (each takes a slice of the result columns)."""
+    if LATENT_TC_PAIRED:
+        return -(-rank // (64 if rank <= 64 else 128 if rank <= 128 else 256 if rank <= 256 else 512))
+    return -(-rank // (64 if rank <= 64 else 128 if rank <= 128 else 256))
 
 
 def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, rot_dims: int,
                      cache: torch.Tensor, block_table: torch.Tensor, cu_q: torch.Tensor, kv_before: torch.Tensor,
                      tile_seq: torch.Tensor, tile_row0: torch.Tensor, n_tiles: int, out: torch.Tensor, *, scale: float,
                      window: int, tensor_cores: bool = False, n_splits: int = 1,
-                     part: torch.Tensor | None = None) -> torch.Tensor:
+                     part: torch.Tensor | None = None, paired: bool | None = None) -> torch.Tensor:
     """q_lat [T, nh, rank] float32, q_rot [T, nh, rot] (unrotated), out [T, nh, rank]: any strides with a unit last
     one; cache [pages, page, 1, rank + rot]. Tiles of 32 (token, head) rows, or of 64 with ``tensor_cores``
     (bfloat16, mma.sync; see ``latent_attention_tc_ok``); that kernel may deal a tile's keys out in ``n_splits``
@@ -892,7 +900,7 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, cos: torch.Tensor
                  _req(cu_q, "cu_q", torch.int32), _req(kv_before, "kv_before", torch.int32),
                  _req(tile_seq, "tile_seq", torch.int32), _req(tile_row0, "tile_row0", torch.int32), n_tiles, out.data_ptr(),
                  out.stride(0), out.stride(1), nh, rank, rot, cache.shape[1], float(scale), int(window), int(n_splits),
-                 _opt(part, "part", torch.float32), _stream())
+                 _opt(part, "part", torch.float32), int(LATENT_TC_PAIRED if paired is None else paired), _stream())
         return out
     lib.call("tm_latent_attention", _code(dt), q_lat.data_ptr(), q_lat.stride(0), q_lat.stride(1), q_rot.data_ptr(),
              q_rot.stride(0), q_rot.stride(1), _req(cos, "cos", torch.float32), _req(sin, "sin", torch.float32), rot_dims,

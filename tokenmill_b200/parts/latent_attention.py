@@ -110,7 +110,7 @@ class LatentAttention:
         # (A captured graph serves every context: it takes the split for the longest.)
         n_tiles, splits = int(tile_seq.size), 1
         if self.tensor_cores and n_tiles:
-            chunks = -(-self.rank // (64 if self.rank <= 64 else 128 if self.rank <= 128 else 256))
+            chunks = ops.latent_attention_tc_chunks(self.rank)
             if shape.for_graph:
                 longest = shape.max_kv_len
             else:
