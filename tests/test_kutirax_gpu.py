@@ -207,6 +207,8 @@ def test_latent_attention_kernels(nh, rank, rot, rot_dims, window, page):
         got = out.transpose(0, 1).float().cpu().double()
         err = float((got - ref).abs().max())
         assert err < 2e-2, (tc, splits, paired, err)
+        if part is not None:
+            part.zero_()             # (the allocator hands this memory to later tests)
 
 
 @pytest.mark.parametrize("top,E", [(1, 5), (3, 12), (4, 4), (2, 37)])
