@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(256) conv_silu_state_kernel(
 template <typename T, int VEC, int TAPS>
 __global__ void __launch_bounds__(128) conv_silu_state_vec_kernel(
     const T* __restrict__ proj, long long proj_stride, int col0, int channels, int taps,
-    const float* __restrict__ weight, const float* __restrict__ bias, float* __restrict__ state,
+    const float* __restrict__ weight, const float* __restrict__ weight_t, const float* __restrict__ bias, float* __restrict__ state,
     long long state_stride, const int* __restrict__ cu_q, const int* __restrict__ seq_of_token,
     const int* __restrict__ state_slots, T* __restrict__ out) {
   pdl_launch_dependents();
@@ -98,11 +98,22 @@ __global__ void __launch_bounds__(128) conv_silu_state_vec_kernel(
   const int carried = taps - 1;
   if (j > 0 && j < carried) return;
   if (j >= carried) {
-    float acc[VEC], wr[VEC * TAPS];          // the thread's VEC x TAPS weights lie side by side: 16 bytes per load
+    // The weights come from the copy laid out [taps, channels]: a warp's loads of one tap are one contiguous
+    // kilobyte (from [channels, taps] every lane would touch a line of its own, and the kernel was bound by that).
+    float acc[VEC], wr[VEC * TAPS], bv[VEC];
 #pragma unroll
-    for (int i = 0; i < VEC * TAPS / 4; ++i) {
-      const float4 w4 = *reinterpret_cast<const float4*>(weight + (size_t)c0 * TAPS + 4 * i);
-      wr[4 * i] = w4.x; wr[4 * i + 1] = w4.y; wr[4 * i + 2] = w4.z; wr[4 * i + 3] = w4.w;
+    for (int k = 0; k < TAPS; ++k)
+#pragma unroll
+      for (int i = 0; i < VEC / 4; ++i) {
+        const float4 w4 = *reinterpret_cast<const float4*>(weight_t + (size_t)k * channels + c0 + 4 * i);
+        wr[(4 * i) * TAPS + k] = w4.x; wr[(4 * i + 1) * TAPS + k] = w4.y;
+        wr[(4 * i + 2) * TAPS + k] = w4.z; wr[(4 * i + 3) * TAPS + k] = w4.w;
+      }
+#pragma unroll
+    for (int i = 0; i < VEC / 4; ++i) {
+      float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (bias) b4 = *reinterpret_cast<const float4*>(bias + c0 + 4 * i);
+      bv[4 * i] = b4.x; bv[4 * i + 1] = b4.y; bv[4 * i + 2] = b4.z; bv[4 * i + 3] = b4.w;
     }
 #pragma unroll
     for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
@@ -117,7 +128,7 @@ __global__ void __launch_bounds__(128) conv_silu_state_vec_kernel(
     T* o = reinterpret_cast<T*>(&res);
 #pragma unroll
     for (int e = 0; e < VEC; ++e) {
-      const float a = acc[e] + (bias ? bias[c0 + e] : 0.f);
+      const float a = acc[e] + bv[e];
       o[e] = from_float<T>(a / (1.0f + expf(-a)));
     }
     *reinterpret_cast<uint4*>(out + (size_t)t * channels + c0) = res;
@@ -152,16 +163,18 @@ __global__ void __launch_bounds__(128) conv_silu_state_vec_kernel(
 
 template <typename T>
 int launch_conv_silu_state(const void* proj, long long proj_stride, int col0, int channels, int taps, const float* weight,
-                           const float* bias, float* state, long long state_stride, const int* cu_q,
+                           const float* weight_t, const float* bias, float* state, long long state_stride, const int* cu_q,
                            const int* seq_of_token, const int* state_slots, void* out, int T_, cudaStream_t stream) {
   constexpr int VEC = 16 / sizeof(T);
   const bool aligned = channels % VEC == 0 && col0 % VEC == 0 && proj_stride % VEC == 0 &&
+                       weight_t != nullptr &&
                        ((reinterpret_cast<uintptr_t>(proj) | reinterpret_cast<uintptr_t>(out) |
-                         reinterpret_cast<uintptr_t>(weight)) & 15) == 0;
+                         reinterpret_cast<uintptr_t>(weight_t) | reinterpret_cast<uintptr_t>(bias)) & 15) == 0;
 #define TM_CONV_VEC(TAPS)                                                                                            \
   if (aligned && taps == TAPS)                                                                                       \
     return launch_pdl(conv_silu_state_vec_kernel<T, VEC, TAPS>, dim3(T_, (channels / VEC + 127) / 128), dim3(128), 0,  \
-                      stream, (const T*)proj, proj_stride, col0, channels, taps, weight, bias, state, state_stride,  \
+                      stream, (const T*)proj, proj_stride, col0, channels, taps, weight, weight_t, bias, state,      \
+                      state_stride,                                                                                  \
                       cu_q, seq_of_token, state_slots, (T*)out);
   TM_CONV_VEC(2) TM_CONV_VEC(3) TM_CONV_VEC(4)
 #undef TM_CONV_VEC
@@ -381,19 +394,20 @@ int launch_ssm_scan(const void* xbc, int channels, const void* proj, long long p
 
 }  // namespace tmk
 
-// proj [T, proj_stride] dtype, channels col0 .. col0 + channels - 1 are convolved; weight [channels, taps], bias
+// proj [T, proj_stride] dtype, channels col0 .. col0 + channels - 1 are convolved; weight [channels, taps] (weight_t:
+// the same as [taps, channels], or null), bias
 // [channels] float; state [slots, state_stride] float, carried inputs first; out [T, channels] dtype.
 extern "C" int tm_conv_silu_state(int dtype, const void* proj, long long proj_stride, int col0, int channels, int taps,
-                                  const float* weight, const float* bias, float* state, long long state_stride,
+                                  const float* weight, const float* weight_t, const float* bias, float* state, long long state_stride,
                                   const int* cu_q, const int* seq_of_token, const int* state_slots, void* out, int T,
                                   cudaStream_t stream) {
   if (T <= 0) return 0;
   if (taps < 1 || taps > tmk::kMaxTaps) return TM_ERR_UNSUPPORTED_SHAPE;
   if (dtype == TM_DTYPE_F32)
-    return tmk::launch_conv_silu_state<float>(proj, proj_stride, col0, channels, taps, weight, bias, state, state_stride,
+    return tmk::launch_conv_silu_state<float>(proj, proj_stride, col0, channels, taps, weight, weight_t, bias, state, state_stride,
                                               cu_q, seq_of_token, state_slots, out, T, stream);
   if (dtype == TM_DTYPE_BF16)
-    return tmk::launch_conv_silu_state<__nv_bfloat16>(proj, proj_stride, col0, channels, taps, weight, bias, state,
+    return tmk::launch_conv_silu_state<__nv_bfloat16>(proj, proj_stride, col0, channels, taps, weight, weight_t, bias, state,
                                                       state_stride, cu_q, seq_of_token, state_slots, out, T, stream);
   return TM_ERR_BAD_DTYPE;
 }

@@ -75,7 +75,7 @@ _SIGNATURES: dict[str, list] = {
                             _I, _I, _I, _I, _F, _I, _P],
     "tm_latent_attention_mma_bf16": [_P, _LL, _LL, _P, _LL, _LL, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _P, _LL, _LL,
                                      _I, _I, _I, _I, _F, _I, _I, _P, _I, _P],
-    "tm_conv_silu_state": [_I, _P, _LL, _I, _I, _I, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _P],
+    "tm_conv_silu_state": [_I, _P, _LL, _I, _I, _I, _P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _P],
     "tm_ssm_scan": [_I, _P, _I, _P, _LL, _I, _P, _P, _P, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P],
     "tm_ssm_pass_states": [_P, _LL, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "tm_relu2": [_I, _P, _P, _LL, _P],

@@ -936,16 +936,20 @@ def bmm_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 
 def conv_silu_state(proj: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: torch.Tensor | None,
                     state: torch.Tensor, cu_q: torch.Tensor, seq_of_token: torch.Tensor, state_slots: torch.Tensor,
-                    out: torch.Tensor) -> torch.Tensor:
+                    out: torch.Tensor, weight_t: torch.Tensor | None = None) -> torch.Tensor:
     """Causal convolution + silu over columns col0 .. col0 + channels of proj [T, P]; weight [channels, taps] float32;
-    the request's last taps - 1 inputs live at the start of its slot of ``state`` [slots, n] float32."""
+    the request's last taps - 1 inputs live at the start of its slot of ``state`` [slots, n] float32. ``weight_t``: the
+    weights once more as [taps, channels], which the 16-bytes-per-access kernel reads."""
+    if weight_t is not None and tuple(weight_t.shape) != (weight.shape[1], weight.shape[0]):
+        raise lib.KernelError("conv_silu_state: weight_t is weight transposed")
     T = proj.shape[0]
     taps = weight.shape[1]
     if weight.shape[0] != channels or out.shape != (T, channels) or state.shape[1] < (taps - 1) * channels or \
             col0 + channels > proj.shape[1]:
         raise lib.KernelError("conv_silu_state: shapes do not fit")
     lib.call("tm_conv_silu_state", _code(proj.dtype), _req(proj, "proj"), proj.stride(0), col0, channels, taps,
-             _req(weight, "weight", torch.float32), _opt(bias, "bias", torch.float32), _req(state, "state", torch.float32),
+             _req(weight, "weight", torch.float32), _opt(weight_t, "weight_t", torch.float32),
+             _opt(bias, "bias", torch.float32), _req(state, "state", torch.float32),
              state.stride(0), _req(cu_q, "cu_q", torch.int32), _req(seq_of_token, "seq_of_token", torch.int32),
              _req(state_slots, "state_slots", torch.int32), _req(out, "out", proj.dtype), T, _stream())
     return out

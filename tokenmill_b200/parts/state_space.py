@@ -23,6 +23,8 @@ from .spec import StateNeed, WeightSpec
 
 SLICED_FROM = 256       # a step whose longest portion has this many tokens runs the recurrence over time slices
 SLICE_LEN = 128
+VECTOR_CONV_FROM = 16   # steps whose longest portion is shorter are mostly rows that own a slot: a thread per channel
+                        # (8 decoded tokens at 2,560 channels: 5 us against 14 with eight channels a thread)
 
 
 class StateSpaceMixer:
@@ -44,7 +46,7 @@ class StateSpaceMixer:
         self.dtype, self.device = dtype, device
         self.names = {"in": "in", "conv": "conv", "conv_bias": "conv.b", "dt_bias": "dt_bias", "A_log": "A_log", "D": "D",
                       "norm": "norm", "o": "o", **(names or {})}
-        self.w_in = self.w_conv = self.b_conv = self.dt_bias = self.A_log = self.D = self.g = self.w_o = None
+        self.w_in = self.w_conv = self.w_conv_t = self.b_conv = self.dt_bias = self.A_log = self.D = self.g = self.w_o = None
 
     def weight_specs(self) -> list[WeightSpec]:
         n, H = self.names, self.hidden_size
@@ -72,6 +74,7 @@ class StateSpaceMixer:
         n = self.names
         self.w_in, self.w_o = tensors[n["in"]], tensors[n["o"]]
         self.w_conv, self.b_conv = tensors[n["conv"]], tensors[n["conv_bias"]]
+        self.w_conv_t = self.w_conv.t().contiguous()          # [taps, channels], for the kernel's 16-byte loads
         self.dt_bias, self.A_log, self.D, self.g = tensors[n["dt_bias"]], tensors[n["A_log"]], tensors[n["D"]], tensors[n["norm"]]
 
     def forward(self, x: torch.Tensor, step: StepInputs, cache: LayerCache) -> torch.Tensor:
@@ -79,7 +82,8 @@ class StateSpaceMixer:
         proj = ops.linear(x, self.w_in)                                       # [T, z | x | B | C | dt]
         xbc = torch.empty((T, self.channels), dtype=self.dtype, device=dev)
         ops.conv_silu_state(proj, self.inner, self.channels, self.w_conv, self.b_conv, cache.state, step.cu_q,
-                            step.seq_of_token, step.state_slots, xbc)
+                            step.seq_of_token, step.state_slots, xbc,
+                            weight_t=self.w_conv_t if step.max_q_len >= VECTOR_CONV_FROM else None)
         y = torch.empty((T, self.inner), dtype=torch.float32, device=dev)
         # Long portions: three passes over time slices instead of one walk over the whole portion (kernels/ops.py).
         sliced = {}
