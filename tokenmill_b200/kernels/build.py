@@ -1,7 +1,11 @@
-"""Compile the sm_100a kernels with nvcc into one shared library, at first use.
+"""Compile the sm_100a kernels with nvcc into shared libraries, at first use.
 
 The sources under ``tokenmill_b200/csrc`` have no dependency beyond the CUDA toolkit (no torch or
-pybind headers), so a cold build takes well under a minute. The library is written next to the
+pybind headers), so a cold build takes well under a minute. They form two libraries, each built when a
+kernel of it is first called, so that a model compiles what it runs and no more: ``main`` (everything the
+Qwen2 path, the sampler and the shape-generic kernels need) and ``hybrid`` (the kernels of latent attention,
+state-space layers, routed experts, 32-bit pair norms, and the 32-bit matrix product, which is in both).
+A library is written next to the
 sources (``csrc/_build``) when that folder can be written, else under the system's temporary folder;
 its name carries a hash of the sources and flags, so an edited source is rebuilt and a stale library
 is never loaded. While nvcc runs, a line is printed to stderr every few seconds.
@@ -38,8 +42,20 @@ def find_nvcc() -> str:
                            "engine has no path that runs without its compiled sm_100a kernels")
 
 
-def sources() -> list[Path]:
-    return sorted(CSRC.glob("*.cu"))
+# Files of the ``hybrid`` library; ``main`` is every other .cu file. SHARED files are compiled into both.
+HYBRID = ("norm_pair.cu", "latent_attention.cu", "latent_attention_mma_bf16.cu", "ssm_scan.cu", "routed_ffn.cu")
+SHARED = ("gemm_f32.cu",)
+GROUPS = ("main", "hybrid")
+_PREFIX = {"main": "libtokenmill_kernels_", "hybrid": "libtokenmill_hybrid_"}
+
+
+def sources(group: str = "main") -> list[Path]:
+    if group not in GROUPS:
+        raise KernelBuildError(f"unknown kernel library {group!r}; known: {GROUPS}")
+    files = sorted(CSRC.glob("*.cu"))
+    if group == "hybrid":
+        return [f for f in files if f.name in HYBRID or f.name in SHARED]
+    return [f for f in files if f.name not in HYBRID]
 
 
 def _digest(files: list[Path]) -> str:
@@ -67,9 +83,9 @@ def _build_dir() -> Path:
     raise KernelBuildError(f"no writable folder for the kernel library (tried {[str(c) for c in cands]})")
 
 
-def library_path() -> Path:
+def library_path(group: str = "main") -> Path:
     """Where the library for the present sources lives (it may not be built yet)."""
-    return _build_dir() / f"libtokenmill_kernels_{_digest(sources())}.so"
+    return _build_dir() / f"{_PREFIX[group]}{_digest(sources(group))}.so"
 
 
 def _run(cmd: list[str]) -> None:
@@ -78,13 +94,18 @@ def _run(cmd: list[str]) -> None:
         raise KernelBuildError(f"nvcc failed ({proc.returncode}): {' '.join(cmd)}\n{proc.stdout}")
 
 
-def build(verbose: bool = True, force: bool = False) -> Path:
+def build_all(verbose: bool = True, force: bool = False) -> list[Path]:
+    """Build every library (the build check; a run builds only what it calls)."""
+    return [build(verbose, force, group) for group in GROUPS]
+
+
+def build(verbose: bool = True, force: bool = False, group: str = "main") -> Path:
     """Build the library if it is missing; return its path."""
-    files = sources()
+    files = sources(group)
     if not files:
         raise KernelBuildError(f"no .cu sources in {CSRC}")
     out_dir = _build_dir()
-    lib = out_dir / f"libtokenmill_kernels_{_digest(files)}.so"
+    lib = out_dir / f"{_PREFIX[group]}{_digest(files)}.so"
     if lib.exists() and not force:
         return lib
     nvcc = find_nvcc()
@@ -95,11 +116,11 @@ def build(verbose: bool = True, force: bool = False) -> Path:
 
     def heartbeat() -> None:
         while not done.wait(5.0):
-            print(f"[tokenmill_b200] compiling sm_100a kernels ({len(files)} files) ... {time.time() - t0:.0f} s",
+            print(f"[tokenmill_b200] compiling sm_100a kernels ({group}: {len(files)} files) ... {time.time() - t0:.0f} s",
                   file=sys.stderr, flush=True)
 
     if verbose:
-        print(f"[tokenmill_b200] compiling sm_100a kernels ({len(files)} files) into {lib}", file=sys.stderr,
+        print(f"[tokenmill_b200] compiling sm_100a kernels ({group}: {len(files)} files) into {lib}", file=sys.stderr,
               flush=True)
         threading.Thread(target=heartbeat, daemon=True).start()
     try:
@@ -112,7 +133,7 @@ def build(verbose: bool = True, force: bool = False) -> Path:
         tmp = out_dir / f".{lib.name}.{os.getpid()}.tmp"
         _run([nvcc, *ARCH_FLAGS, "-shared", "-o", str(tmp), *[str(o) for o in objs], "-lcuda", "-ldl"])
         os.replace(tmp, lib)  # atomic: a concurrent builder never sees half a library
-        for stale in out_dir.glob("libtokenmill_kernels_*.so"):     # libraries of earlier source states
+        for stale in out_dir.glob(_PREFIX[group] + "*.so"):         # libraries of earlier source states
             if stale != lib:
                 stale.unlink(missing_ok=True)   # a process that has one mapped keeps its copy
     finally:

@@ -28,7 +28,7 @@ _REFUSALS = {
 }
 
 _lock = threading.Lock()
-_lib: ctypes.CDLL | None = None
+_libs: dict[str, ctypes.CDLL] = {}          # by library (kernels/build.py: "main", "hybrid"), loaded on first use
 launch_count = 0
 
 _P, _I, _F, _LL = c_void_p, c_int, c_float, c_longlong
@@ -87,11 +87,25 @@ _SIGNATURES: dict[str, list] = {
 }
 
 
+# Entry points of the "hybrid" library; everything else is in "main". The 32-bit matrix product is in both and is
+# taken from whichever is loaded (a model that needs only one library builds only that one).
+_HYBRID = {"tm_add_norm_pair", "tm_token_shift", "tm_gated_group_norm", "tm_latent_prepare", "tm_latent_attention",
+           "tm_latent_attention_mma_bf16", "tm_conv_silu_state", "tm_ssm_scan", "tm_ssm_pass_states", "tm_relu2",
+           "tm_moe_topk", "tm_glu_routed", "tm_gemm_f32_nt_batched"}
+_BOTH = {"tm_gemm_f32_nt"}
+
+
+def _group_of(name: str) -> str:
+    if name in _BOTH:
+        return "main" if "main" in _libs else "hybrid"          # (neither loaded yet: the small one)
+    return "hybrid" if name in _HYBRID else "main"
+
+
 def register_signature(name: str, argtypes: list) -> None:
-    """Declare one more exported entry point (used by kernel files added later)."""
+    """Declare one more exported entry point of the main library (used by kernel files added later)."""
     _SIGNATURES[name] = argtypes
-    if _lib is not None:
-        _bind(_lib, name, argtypes)
+    if "main" in _libs:
+        _bind(_libs["main"], name, argtypes)
 
 
 def _bind(lib: ctypes.CDLL, name: str, argtypes: list) -> None:
@@ -103,29 +117,34 @@ def _bind(lib: ctypes.CDLL, name: str, argtypes: list) -> None:
     fn.restype = c_int
 
 
-def load() -> ctypes.CDLL:
-    """Build (if needed) and load the library. Raises if that is impossible."""
-    global _lib
-    if _lib is not None:
-        return _lib
+def load(group: str = "main") -> ctypes.CDLL:
+    """Build (if needed) and load one of the libraries. Raises if that is impossible."""
+    lib = _libs.get(group)
+    if lib is not None:
+        return lib
     with _lock:
-        if _lib is None:
-            path = _build.build()
+        if group not in _libs:
+            path = _build.build(group=group)
             lib = ctypes.CDLL(str(path))
             for name, argtypes in _SIGNATURES.items():
-                _bind(lib, name, argtypes)
-            _lib = lib
-    return _lib
+                if name in _BOTH or (name in _HYBRID) == (group == "hybrid"):
+                    _bind(lib, name, argtypes)
+            _libs[group] = lib
+    return _libs[group]
 
 
-def library_file() -> str:
-    return str(_build.library_path())
+def library_file(group: str = "main") -> str:
+    return str(_build.library_path(group))
+
+
+def loaded_libraries() -> list[str]:
+    return [library_file(g) for g in _libs]
 
 
 def call(name: str, *args) -> None:
     """Call an entry point; a non-zero status raises."""
     global launch_count
-    lib = load()
+    lib = load(_group_of(name))
     status = getattr(lib, name)(*args)
     launch_count += 1
     if status != 0:
