@@ -1,5 +1,5 @@
 // Attention over a cache of latents on the tensor cores (bfloat16 operands, 32-bit accumulation), for prompt
-// portions and decoded tokens alike. Same contract as tm_latent_attention (latent_attention.cu): every token's cache
+// portions and decoded tokens alike. Same interface as tm_latent_attention (latent_attention.cu): every token's cache
 // row is [c (rank) | k_rot (rot)], a query row is [q_lat (rank) | rope(q_rot) (rot)], the score is their dot product
 // times scale over the last `window` positions, and the result is the softmax-weighted sum of the c rows.
 //
