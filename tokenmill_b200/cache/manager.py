@@ -91,9 +91,14 @@ def chain_hash(parent: int | None, tokens: list[int]) -> int:
 
 class CacheManager:
     def __init__(self, num_pages: int | list[int], page_size: int, windows: list[int | None] | None = None,
-                 watermark: float = 0.01, enable_prefix_caching: bool = False, num_state_slots: int = 0):
+                 watermark: float = 0.01, enable_prefix_caching: bool = False, num_state_slots: int = 0,
+                 keep_first: list[int] | None = None):
         self.windows = list(windows) if windows is not None else [None]
         self.num_groups = len(self.windows)
+        # windowed groups whose queries also read a sequence's first positions: the pages of those are never given back
+        self.keep_first = list(keep_first) if keep_first is not None else [0] * self.num_groups
+        if len(self.keep_first) != self.num_groups:
+            raise ValueError("one keep_first per group")
         pages = num_pages if isinstance(num_pages, list) else [num_pages] * self.num_groups
         if len(pages) != self.num_groups:
             raise ValueError("one page count per group")
@@ -210,14 +215,16 @@ class CacheManager:
 
     def release_behind_window(self, handle: CacheHandle, num_computed: int) -> int:
         """Give back, in windowed groups, the pages no future query can read: page i goes once
-        (i + 1) * page_size <= num_computed - window + 1. Returns how many pages were released."""
+        (i + 1) * page_size <= num_computed - window + 1, unless it holds one of the group's kept first positions
+        (i * page_size < keep_first). Returns how many pages were released."""
         released = 0
         for g, window in enumerate(self.windows):
             if window is None:
                 continue
             dead = max(0, (num_computed - window + 1)) // self.page_size
             table = handle.tables[g]
-            for i in range(min(dead, len(table))):
+            kept = self.pages_for(self.keep_first[g])
+            for i in range(kept, min(dead, len(table))):
                 if table[i] >= 0:
                     self.allocators[g].release([table[i]])
                     table[i] = -1

@@ -1,0 +1,235 @@
+// Kernels of a pre-norm block whose branches enter the stream through a learned gate and whose sublayers read their
+// input through a short causal convolution, plus the small kernels its branches need. All arithmetic is 32-bit;
+// every output is rounded once.
+//
+// tm_gated_add_rmsnorm, one block per row:
+//   x = table[ids[row]] * table_scale                     (the stream starts here), or
+//   x = resid[row] + sigmoid(gate[row] + gate_bias) * branch[row]      (gate absent: the branch is added as it is)
+//   out[row] = x / sqrt(mean(x^2) + eps) * w
+// `gate` is the gate's pre-activation as a 32-bit matrix product result. With `rows`, only those rows are normed,
+// written densely, and the stream is left as it is.
+//
+// tm_canon_conv, one block per row: out[t] = h[t] + sum_j w[:, j] h[t - taps + 1 + j]. Rows before the step's first row
+// of a request come from the request's state slot (its last taps - 1 inputs, oldest first; zeros for a new request).
+// The block of a request's first row computes every row that still reads the slot (the first taps - 1 of the step) and
+// then writes the step's last taps - 1 inputs back, a thread per channel doing both: nothing else touches the slot.
+//
+// tm_glu: out[t, i] = act(gu[t, i]) * gu[t, I + i], act = silu or the tanh form of gelu.
+//
+// tm_norm_pair_mean: out = (rmsnorm(a) wa + rmsnorm(b) wb) / 2, each row of a and b by its own root mean square.
+//
+// tm_head_norm_gate: y [T, heads, dv] float32 -> each head divided by its root mean square, times weight, times
+// sigmoid(gate pre-activation read from a 32-bit product).
+#include "common.cuh"
+
+namespace tmk {
+
+template <typename T>
+__global__ void __launch_bounds__(256) gated_add_rmsnorm_kernel(
+    float* __restrict__ resid, const T* __restrict__ branch, const float* __restrict__ gate, long long gate_stride,
+    const float* __restrict__ gate_bias, const int* __restrict__ ids, const T* __restrict__ table, float table_scale,
+    const int* __restrict__ rows, const float* __restrict__ w, float eps, T* __restrict__ out, int H) {
+  extern __shared__ __align__(16) float xs[];  // H floats + 32 for the reduction
+  float* red = xs + H;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  const bool write_back = !rows && (ids || branch);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float x;
+    if (ids) {
+      x = to_float(table[(size_t)ids[src] * H + i]) * table_scale;
+    } else {
+      x = resid[(size_t)src * H + i];
+      if (branch) {
+        const float y = to_float(branch[(size_t)src * H + i]);
+        if (gate) {
+          const float z = gate[(size_t)src * gate_stride + i] + (gate_bias ? gate_bias[i] : 0.f);
+          x += y / (1.0f + expf(-z));
+        } else {
+          x += y;
+        }
+      }
+    }
+    if (write_back) resid[(size_t)src * H + i] = x;
+    xs[i] = x;
+    ss += x * x;
+  }
+  const float total = block_sum(ss, red);
+  const float rstd = 1.0f / sqrtf(total / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)r * H + i] = from_float<T>(xs[i] * rstd * w[i]);
+}
+
+constexpr int kMaxTaps = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(256) canon_conv_kernel(
+    const T* __restrict__ h, const float* __restrict__ w, float* __restrict__ state, long long state_stride,
+    const int* __restrict__ cu_q, const int* __restrict__ seq_of_token, const int* __restrict__ state_slots,
+    T* __restrict__ out, int C, int taps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int s = seq_of_token[t];
+  const int first = cu_q[s], end = cu_q[s + 1];
+  const int local = t - first;
+  const int carry = taps - 1;
+  if (local >= carry) {                     // every tap lies inside the step
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+      float acc = 0.f;
+      for (int j = 0; j < taps; ++j) acc = fmaf(w[(size_t)c * taps + j], to_float(h[(size_t)(t - carry + j) * C + c]), acc);
+      out[(size_t)t * C + c] = from_float<T>(to_float(h[(size_t)t * C + c]) + acc);
+    }
+    return;
+  }
+  if (local != 0) return;                   // the first row's block does these rows
+  float* slot = state + (size_t)state_slots[s] * state_stride;
+  const int n = end - first;
+  const int head = min(n, carry);
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float old[kMaxTaps], wt[kMaxTaps];
+    for (int j = 0; j < carry; ++j) old[j] = slot[(size_t)j * C + c];
+    for (int j = 0; j < taps; ++j) wt[j] = w[(size_t)c * taps + j];
+    for (int r = 0; r < head; ++r) {        // row first + r reads positions r - carry .. r of the step
+      float acc = 0.f;
+      for (int j = 0; j < taps; ++j) {
+        const int p = r - carry + j;        // p < 0: slot entry carry + p
+        const float v = p < 0 ? old[carry + p] : to_float(h[(size_t)(first + p) * C + c]);
+        acc = fmaf(wt[j], v, acc);
+      }
+      out[(size_t)(first + r) * C + c] = from_float<T>(to_float(h[(size_t)(first + r) * C + c]) + acc);
+    }
+    for (int j = 0; j < carry; ++j) {       // the last `carry` inputs of (old inputs ++ this step's)
+      const int p = n - carry + j;
+      slot[(size_t)j * C + c] = p < 0 ? old[carry + p] : to_float(h[(size_t)(first + p) * C + c]);
+    }
+  }
+}
+
+__device__ __forceinline__ float gelu_tanh(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename T, int ACT>
+__global__ void __launch_bounds__(256) glu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long t = blockIdx.x;
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= I) return;
+  const float g = to_float(gu[t * 2 * I + i]), u = to_float(gu[t * 2 * I + I + i]);
+  const float a = ACT == 0 ? g / (1.0f + expf(-g)) : gelu_tanh(g);
+  out[t * I + i] = from_float<T>(a * u);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) norm_pair_mean_kernel(const T* __restrict__ a, const T* __restrict__ b,
+                                                             const float* __restrict__ wa, const float* __restrict__ wb,
+                                                             float eps, T* __restrict__ out, int H) {
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t row = (size_t)blockIdx.x * H;
+  float sa = 0.f, sb = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float x = to_float(a[row + i]), y = to_float(b[row + i]);
+    sa += x * x;
+    sb += y * y;
+  }
+  const float ra = 1.0f / sqrtf(block_sum(sa, red) / (float)H + eps);
+  const float rb = 1.0f / sqrtf(block_sum(sb, red) / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    out[row + i] = from_float<T>(0.5f * (to_float(a[row + i]) * ra * wa[i] + to_float(b[row + i]) * rb * wb[i]));
+}
+
+// One warp per (row, head).
+template <typename T>
+__global__ void __launch_bounds__(128) head_norm_gate_kernel(const float* __restrict__ y, const float* __restrict__ gate,
+                                                             long long gate_stride, const float* __restrict__ w, float eps,
+                                                             T* __restrict__ out, int heads, int dv, long long n_pairs) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long pair = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (pair >= n_pairs) return;
+  const int lane = threadIdx.x & 31;
+  const long long t = pair / heads;
+  const int hd = (int)(pair - t * heads);
+  const float* src = y + (size_t)pair * dv;
+  float ss = 0.f;
+  for (int i = lane; i < dv; i += 32) ss += src[i] * src[i];
+  const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
+  for (int i = lane; i < dv; i += 32) {
+    const int c = hd * dv + i;
+    const float z = gate[(size_t)t * gate_stride + c];
+    out[(size_t)pair * dv + i] = from_float<T>(src[i] * rstd * w[c] / (1.0f + expf(-z)));
+  }
+}
+
+}  // namespace tmk
+
+using namespace tmk;
+
+#define TM_BY_DTYPE(dtype, ...)                                              \
+  if ((dtype) == TM_DTYPE_F32) { using T = float; __VA_ARGS__; }             \
+  if ((dtype) == TM_DTYPE_BF16) { using T = __nv_bfloat16; __VA_ARGS__; }    \
+  return TM_ERR_BAD_DTYPE;
+
+// resid [T, H] float; branch [T, H] dtype or null; gate: float, row stride gate_stride, or null; gate_bias [H] float or
+// null; ids [T] + table [V, H] dtype or null; rows [n_rows] or null; w [H] float; out [n_rows, H] dtype.
+extern "C" int tm_gated_add_rmsnorm(int dtype, float* resid, const void* branch, const float* gate, long long gate_stride,
+                                    const float* gate_bias, const int* ids, const void* table, float table_scale,
+                                    const int* rows, const float* w, float eps, void* out, int n_rows, int H,
+                                    cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  const size_t smem = (size_t)(H + 32) * sizeof(float);
+  if (smem > 200 * 1024) return TM_ERR_UNSUPPORTED_SHAPE;
+  TM_BY_DTYPE(dtype, {
+    auto kern = gated_add_rmsnorm_kernel<T>;
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    return launch_pdl(kern, dim3(n_rows), dim3(256), smem, stream, resid, (const T*)branch, gate, gate_stride, gate_bias,
+                      ids, (const T*)table, table_scale, rows, w, eps, (T*)out, H);
+  })
+}
+
+// h, out [T, C] dtype; w [C, taps] float; state: float, a request's slot starts at state + slot * state_stride and holds
+// [taps - 1, C] there.
+extern "C" int tm_canon_conv(int dtype, const void* h, const float* w, float* state, long long state_stride,
+                             const int* cu_q, const int* seq_of_token, const int* state_slots, void* out, int T_rows, int C,
+                             int taps, cudaStream_t stream) {
+  if (T_rows <= 0) return 0;
+  if (taps < 1 || taps > kMaxTaps) return TM_ERR_UNSUPPORTED_SHAPE;
+  TM_BY_DTYPE(dtype, return launch_pdl(canon_conv_kernel<T>, dim3(T_rows), dim3(256), 0, stream, (const T*)h, w, state,
+                                       state_stride, cu_q, seq_of_token, state_slots, (T*)out, C, taps))
+}
+
+// gu [T, 2 I] (gate columns first) -> out [T, I]; act 0: silu, 1: gelu (tanh form).
+extern "C" int tm_glu(int dtype, int act, const void* gu, void* out, int T_rows, int I, cudaStream_t stream) {
+  if (T_rows <= 0) return 0;
+  if (act != 0 && act != 1) return TM_ERR_UNSUPPORTED_SHAPE;
+  const dim3 grid(T_rows, (I + 255) / 256);
+  TM_BY_DTYPE(dtype, {
+    if (act == 0) return launch_pdl(glu_kernel<T, 0>, grid, dim3(256), 0, stream, (const T*)gu, (T*)out, I);
+    return launch_pdl(glu_kernel<T, 1>, grid, dim3(256), 0, stream, (const T*)gu, (T*)out, I);
+  })
+}
+
+extern "C" int tm_norm_pair_mean(int dtype, const void* a, const void* b, const float* wa, const float* wb, float eps,
+                                 void* out, int T_rows, int H, cudaStream_t stream) {
+  if (T_rows <= 0) return 0;
+  TM_BY_DTYPE(dtype, return launch_pdl(norm_pair_mean_kernel<T>, dim3(T_rows), dim3(256), 0, stream, (const T*)a,
+                                       (const T*)b, wa, wb, eps, (T*)out, H))
+}
+
+// y [T, heads * dv] float; gate: float pre-activations, element (t, c) at gate + t * gate_stride + c; w [heads * dv].
+extern "C" int tm_head_norm_gate(int dtype, const float* y, const float* gate, long long gate_stride, const float* w,
+                                 float eps, void* out, int T_rows, int heads, int dv, cudaStream_t stream) {
+  if (T_rows <= 0) return 0;
+  const long long pairs = (long long)T_rows * heads;
+  TM_BY_DTYPE(dtype, return launch_pdl(head_norm_gate_kernel<T>, dim3((unsigned)((pairs + 3) / 4)), dim3(128), 0, stream, y,
+                                       gate, gate_stride, w, eps, (T*)out, heads, dv, pairs))
+}

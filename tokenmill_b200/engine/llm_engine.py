@@ -110,7 +110,7 @@ class LLMEngine:
         n_groups = len(layout.groups)
         n_state = cfg.max_num_seqs if layout.has_state else 0
         self.cache = CacheManager([num_pages] * n_groups, cfg.block_size, layout.windows, cfg.watermark,
-                                  cfg.enable_prefix_caching, num_state_slots=n_state)
+                                  cfg.enable_prefix_caching, num_state_slots=n_state, keep_first=layout.keep_first)
         self.pools = CachePools(layout, [num_pages] * n_groups, cfg.block_size, self.dtype, self.device,
                                 num_state_slots=n_state, sink_page=cfg.cuda_graphs,
                                 run_order_cache_of=[e.cache_of for e in model.spec.run_order])

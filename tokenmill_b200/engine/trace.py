@@ -53,7 +53,7 @@ def run(model_dir: str, dtype_name: str, out_dir: str, max_tokens: int, stdin=No
     n_groups = len(layout.groups)
     n_state = state_slots if layout.has_state else 0
     cache = CacheManager([num_pages] * n_groups, page_size, layout.windows, watermark=0.0,
-                         enable_prefix_caching=False, num_state_slots=n_state)
+                         enable_prefix_caching=False, num_state_slots=n_state, keep_first=layout.keep_first)
     pools = CachePools(layout, [num_pages] * n_groups, page_size, dtype, dev, num_state_slots=n_state,
                        run_order_cache_of=[e.cache_of for e in model.spec.run_order])
     runner = ModelRunner(model, cache, pools, max_model_len=model.max_positions())

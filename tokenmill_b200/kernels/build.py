@@ -1,7 +1,7 @@
 """Compile the sm_100a kernels with nvcc into shared libraries, at first use.
 
 The sources under ``tokenmill_b200/csrc`` have no dependency beyond the CUDA toolkit (no torch or
-pybind headers), so a cold build takes well under a minute. They form two libraries, each built when a
+pybind headers), so a cold build takes well under a minute. They form three libraries, each built when a
 kernel of it is first called, so that a model compiles what it runs and no more: ``main`` (everything the
 Qwen2 path, the sampler and the shape-generic kernels need) and ``hybrid`` (the kernels of latent attention,
 state-space layers, routed experts, 32-bit pair norms, and the 32-bit matrix product, which is in both).
@@ -42,20 +42,22 @@ def find_nvcc() -> str:
                            "engine has no path that runs without its compiled sm_100a kernels")
 
 
-# Files of the ``hybrid`` library; ``main`` is every other .cu file. SHARED files are compiled into both.
+# Files of the ``hybrid`` and ``gated`` libraries; ``main`` is every other .cu file. SHARED files are compiled into all.
 HYBRID = ("norm_pair.cu", "latent_attention.cu", "latent_attention_mma_bf16.cu", "ssm_scan.cu", "routed_ffn.cu")
+GATED = ("gated_block.cu", "sink_attention.cu", "matrix_memory.cu")
 SHARED = ("gemm_f32.cu",)
-GROUPS = ("main", "hybrid")
-_PREFIX = {"main": "libtokenmill_kernels_", "hybrid": "libtokenmill_hybrid_"}
+GROUPS = ("main", "hybrid", "gated")
+_PREFIX = {"main": "libtokenmill_kernels_", "hybrid": "libtokenmill_hybrid_", "gated": "libtokenmill_gated_"}
+_FILES = {"hybrid": HYBRID, "gated": GATED}
 
 
 def sources(group: str = "main") -> list[Path]:
     if group not in GROUPS:
         raise KernelBuildError(f"unknown kernel library {group!r}; known: {GROUPS}")
     files = sorted(CSRC.glob("*.cu"))
-    if group == "hybrid":
-        return [f for f in files if f.name in HYBRID or f.name in SHARED]
-    return [f for f in files if f.name not in HYBRID]
+    if group in _FILES:
+        return [f for f in files if f.name in _FILES[group] or f.name in SHARED]
+    return [f for f in files if not any(f.name in names for names in _FILES.values())]
 
 
 def _digest(files: list[Path]) -> str:

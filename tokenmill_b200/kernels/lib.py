@@ -82,23 +82,37 @@ _SIGNATURES: dict[str, list] = {
     "tm_moe_topk": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
     "tm_glu_routed": [_I, _P, _P, _P, _I, _I, _I, _P],
     "tm_gemm_f32_nt_batched": [_P, _LL, _I, _P, _LL, _P, _LL, _I, _I, _I, _I, _I, _P],
+    "tm_gated_add_rmsnorm": [_I, _P, _P, _P, _LL, _P, _P, _P, _F, _P, _P, _F, _P, _I, _I, _P],
+    "tm_canon_conv": [_I, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _P],
+    "tm_glu": [_I, _I, _P, _P, _I, _I, _P],
+    "tm_norm_pair_mean": [_I, _P, _P, _P, _P, _F, _P, _I, _I, _P],
+    "tm_head_norm_gate": [_I, _P, _P, _LL, _P, _F, _P, _I, _I, _I, _P],
+    "tm_qk_norm_rope_write": [_I, _P, _LL, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P],
+    "tm_sink_attention": [_I, _P, _P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P],
+    "tm_matrix_memory": [_P, _LL, _I, _I, _I, _I, _I, _P, _P, _F, _F, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I, _P],
     "tm_argmax": [_P, _I, _I, _LL, _P, _P, _P, _P],
     "tm_sample": [_P, _I, _I, _LL, _P, _P, _P, _P, _P, _P, _I, _P, _P],
 }
 
 
-# Entry points of the "hybrid" library; everything else is in "main". The 32-bit matrix product is in both and is
-# taken from whichever is loaded (a model that needs only one library builds only that one).
+# Entry points of the "hybrid" and "gated" libraries; everything else is in "main". The 32-bit matrix product is in all
+# and is taken from whichever is loaded (a model that needs only one library builds only that one).
 _HYBRID = {"tm_add_norm_pair", "tm_token_shift", "tm_gated_group_norm", "tm_latent_prepare", "tm_latent_attention",
            "tm_latent_attention_mma_bf16", "tm_conv_silu_state", "tm_ssm_scan", "tm_ssm_pass_states", "tm_relu2",
            "tm_moe_topk", "tm_glu_routed", "tm_gemm_f32_nt_batched"}
-_BOTH = {"tm_gemm_f32_nt"}
+_GATED = {"tm_gated_add_rmsnorm", "tm_canon_conv", "tm_glu", "tm_norm_pair_mean", "tm_head_norm_gate",
+          "tm_qk_norm_rope_write", "tm_sink_attention", "tm_matrix_memory"}
+_BOTH = {"tm_gemm_f32_nt"}            # in every library
+
+
+def _home(name: str) -> str:
+    return "hybrid" if name in _HYBRID else "gated" if name in _GATED else "main"
 
 
 def _group_of(name: str) -> str:
-    if name in _BOTH:
-        return "main" if "main" in _libs else "hybrid"          # (neither loaded yet: the small one)
-    return "hybrid" if name in _HYBRID else "main"
+    if name in _BOTH:                 # from whichever library is loaded (none yet: the one last asked for, or the small one)
+        return next(iter(_libs), "hybrid")
+    return _home(name)
 
 
 def register_signature(name: str, argtypes: list) -> None:
@@ -127,7 +141,7 @@ def load(group: str = "main") -> ctypes.CDLL:
             path = _build.build(group=group)
             lib = ctypes.CDLL(str(path))
             for name, argtypes in _SIGNATURES.items():
-                if name in _BOTH or (name in _HYBRID) == (group == "hybrid"):
+                if name in _BOTH or _home(name) == group:
                     _bind(lib, name, argtypes)
             _libs[group] = lib
     return _libs[group]

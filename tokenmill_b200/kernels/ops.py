@@ -1029,3 +1029,163 @@ def glu_routed(gu: torch.Tensor, dense_w: torch.Tensor, act: torch.Tensor, E: in
     lib.call("tm_glu_routed", _code(gu.dtype), _req(gu, "gu"), _req(dense_w, "dense_w", torch.float32),
              _req(act, "act", gu.dtype), T, E, F, _stream())
     return act
+
+
+# --- gated convolutional blocks, windowed attention with a sink, matrix memory --------------------------------
+
+GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def linear32(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x [T, K] . w [N, K]^T with the 32-bit accumulator kept as the result ([T, N] float32) in both run dtypes."""
+    return linear(x, w, out_dtype=torch.float32)
+
+
+def gated_add_rmsnorm(resid: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, *,
+                      branch: torch.Tensor | None = None, gate: torch.Tensor | None = None,
+                      gate_bias: torch.Tensor | None = None, ids: torch.Tensor | None = None,
+                      table: torch.Tensor | None = None, table_scale: float = 1.0,
+                      rows: torch.Tensor | None = None) -> torch.Tensor:
+    """resid [T, H] float32 += sigmoid(gate + gate_bias) * branch (or = table[ids] * table_scale); out = rmsnorm(resid) * w.
+    gate [T, H] float32 (rows may be strided) holds the gate's pre-activations. With ``rows`` only those rows are normed."""
+    H = resid.shape[-1]
+    n_rows = rows.numel() if rows is not None else resid.shape[0]
+    if out.shape[0] < n_rows or out.shape[-1] != H or weight.numel() != H or (ids is None) != (table is None):
+        raise lib.KernelError("gated_add_rmsnorm: shapes do not fit")
+    if gate is not None and (branch is None or gate.dtype != torch.float32 or gate.stride(-1) != 1 or gate.shape[-1] != H):
+        raise lib.KernelError("gated_add_rmsnorm: the gate is a float32 [T, H] beside a branch")
+    dt = out.dtype
+    lib.call("tm_gated_add_rmsnorm", _code(dt), _req(resid, "resid", torch.float32), _opt(branch, "branch", dt),
+             gate.data_ptr() if gate is not None else None, gate.stride(0) if gate is not None else 0,
+             _opt(gate_bias, "gate_bias", torch.float32), _opt(ids, "ids", torch.int32), _opt(table, "table", dt),
+             float(table_scale), _opt(rows, "rows", torch.int32), _req(weight, "weight", torch.float32), float(eps),
+             _req(out, "out"), n_rows, H, _stream())
+    return out
+
+
+def canon_conv(h: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor, seq_of_token: torch.Tensor,
+               state_slots: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = h[t] + sum_j weight[:, j] h[t - taps + 1 + j]; weight [C, taps] float32; ``state`` [slots, (taps - 1) * C]
+    float32 (a view whose rows may be strided) carries each request's last taps - 1 inputs from step to step."""
+    T, C = h.shape
+    taps = weight.shape[1]
+    if weight.shape[0] != C or out.shape != h.shape or state.shape[1] < (taps - 1) * C or state.stride(1) != 1:
+        raise lib.KernelError("canon_conv: shapes do not fit")
+    lib.call("tm_canon_conv", _code(h.dtype), _req(h, "h"), _req(weight, "weight", torch.float32), state.data_ptr(),
+             state.stride(0), _req(cu_q, "cu_q", torch.int32), _req(seq_of_token, "seq_of_token", torch.int32),
+             _req(state_slots, "state_slots", torch.int32), _req(out, "out", h.dtype), T, C, taps, _stream())
+    return out
+
+
+def glu(gu: torch.Tensor, out: torch.Tensor, activation: str) -> torch.Tensor:
+    """gu [T, 2 I] (gate columns first) -> out [T, I] = act(gate) * up, act in GLU_ACTIVATIONS."""
+    T, two_i = gu.shape
+    if two_i % 2 or out.shape != (T, two_i // 2) or activation not in GLU_ACTIVATIONS:
+        raise lib.KernelError(f"glu: gu {tuple(gu.shape)}, out {tuple(out.shape)}, activation {activation!r} do not fit")
+    lib.call("tm_glu", _code(gu.dtype), GLU_ACTIVATIONS[activation], _req(gu, "gu"), _req(out, "out", gu.dtype), T,
+             two_i // 2, _stream())
+    return out
+
+
+def norm_pair_mean(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, eps: float,
+                   out: torch.Tensor) -> torch.Tensor:
+    """out = (rmsnorm(a) * wa + rmsnorm(b) * wb) / 2, row by row."""
+    T, H = a.shape
+    if b.shape != a.shape or out.shape != a.shape or wa.numel() != H or wb.numel() != H:
+        raise lib.KernelError("norm_pair_mean: shapes do not fit")
+    lib.call("tm_norm_pair_mean", _code(a.dtype), _req(a, "a"), _req(b, "b", a.dtype), _req(wa, "wa", torch.float32),
+             _req(wb, "wb", torch.float32), float(eps), _req(out, "out", a.dtype), T, H, _stream())
+    return out
+
+
+def head_norm_gate(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, heads: int,
+                   out: torch.Tensor) -> torch.Tensor:
+    """y [T, heads * dv] float32: each head by its own root mean square, times weight, times sigmoid(gate); gate
+    [T, heads * dv] float32 pre-activations (rows may be strided)."""
+    T, inner = y.shape
+    if inner % heads or gate.shape != y.shape or gate.stride(1) != 1 or gate.dtype != torch.float32 or \
+            weight.numel() != inner or out.shape != y.shape:
+        raise lib.KernelError("head_norm_gate: shapes do not fit")
+    lib.call("tm_head_norm_gate", _code(out.dtype), _req(y, "y", torch.float32), gate.data_ptr(), gate.stride(0),
+             _req(weight, "weight", torch.float32), float(eps), _req(out, "out"), T, heads, inner // heads, _stream())
+    return out
+
+
+def qk_norm_rope_write(proj: torch.Tensor, *, heads: int, kv_heads: int, dim: int, vdim: int, rot_dims: int,
+                       wq: torch.Tensor | None, wk: torch.Tensor | None, eps: float, positions: torch.Tensor,
+                       cos: torch.Tensor, sin: torch.Tensor, slot_map: torch.Tensor | None, q_out: torch.Tensor,
+                       cache: torch.Tensor | None, gate_out: torch.Tensor | None) -> None:
+    """proj [T, >= H d + G d + G dv (+ H)] float32 (rows may be strided) -> q_out [T, H d] normed and rotated, the
+    token's cache row [k | v], gate_out [T, H] = sigmoid of the last H columns."""
+    T = proj.shape[0]
+    need = heads * dim + kv_heads * (dim + vdim) + (heads if gate_out is not None else 0)
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or proj.shape[1] < need or q_out.shape != (T, heads * dim) or \
+            cos.shape[1] * 2 != rot_dims or (cache is not None and cache.shape[-1] != kv_heads * (dim + vdim)):
+        raise lib.KernelError("qk_norm_rope_write: shapes do not fit")
+    dt = q_out.dtype
+    lib.call("tm_qk_norm_rope_write", _code(dt), proj.data_ptr(), proj.stride(0), heads, kv_heads, dim, vdim, rot_dims,
+             _opt(wq, "wq", torch.float32), _opt(wk, "wk", torch.float32), float(eps),
+             _req(positions, "positions", torch.int32), _req(cos, "cos", torch.float32), _req(sin, "sin", torch.float32),
+             cos.shape[0], _opt(slot_map, "slot_map", torch.int32) if cache is not None else None, _req(q_out, "q_out"),
+             _opt(cache, "cache", dt), _opt(gate_out, "gate_out", torch.float32), T, _tc_flag(proj.device).data_ptr(),
+             _stream())
+
+
+SINK_TILE_ROWS = 32
+
+
+def sink_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, cu_q: torch.Tensor,
+                   kv_before: torch.Tensor, tile_seq: torch.Tensor, tile_row0: torch.Tensor, n_tiles: int,
+                   gate: torch.Tensor | None, out: torch.Tensor, *, heads: int, kv_heads: int, dim: int, vdim: int,
+                   scale: float, softcap: float, window: int, keep_first: int, sink: bool) -> torch.Tensor:
+    """q [T, H d]; cache [pages, page_size, 1, G d + G dv]; tiles of 32 (token, head in group) rows of one request;
+    gate [T, H] float32 or None; out [T, H dv]."""
+    T = q.shape[0]
+    row = kv_heads * (dim + vdim)
+    if cache.shape[-1] != row or q.shape != (T, heads * dim) or out.shape != (T, heads * vdim):
+        raise lib.KernelError("sink_attention: shapes do not fit")
+    lib.call("tm_sink_attention", _code(q.dtype), _req(q, "q"), _req(cache, "cache", q.dtype), row, kv_heads * dim,
+             _req(block_table, "block_table", torch.int32), block_table.stride(0), _req(cu_q, "cu_q", torch.int32),
+             _req(kv_before, "kv_before", torch.int32), _req(tile_seq, "tile_seq", torch.int32),
+             _req(tile_row0, "tile_row0", torch.int32), int(n_tiles), _opt(gate, "gate", torch.float32),
+             _req(out, "out", q.dtype), heads, kv_heads, dim, vdim, cache.shape[1], float(scale), float(softcap),
+             int(window), int(keep_first), int(bool(sink)), _stream())
+    return out
+
+
+MEMORY_THREADS = 256
+
+
+def matrix_memory_geometry(dim: int, vdim: int) -> tuple[int, int, int]:
+    """(d_pad, value columns per block, column tiles) of the matrix-memory kernel for heads of dim x vdim: a column's
+    state is spread over ``parts`` lanes of 8, 16 or 32 rows each (csrc/matrix_memory.cu)."""
+    R = 8 if dim <= 256 else 16 if dim <= 512 else 32
+    parts = 1
+    while parts * R < dim:
+        parts *= 2
+    cols = MEMORY_THREADS // parts
+    return parts * R, cols, -(-vdim // cols)
+
+
+def matrix_memory_state_floats(heads: int, dim: int, vdim: int) -> int:
+    d_pad, _cols, tiles = matrix_memory_geometry(dim, vdim)
+    return heads * vdim * d_pad + heads * tiles * (d_pad + 4)
+
+
+def matrix_memory(proj: torch.Tensor, *, q_col: int, k_col: int, v_col: int, i_col: int, f_col: int,
+                  i_bias: torch.Tensor | None, f_bias: torch.Tensor | None, cap: float, q_scale: float,
+                  state: torch.Tensor, state_off: int, cu_q: torch.Tensor, state_slots: torch.Tensor, y: torch.Tensor,
+                  n_seqs: int, heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """The recurrence over this step's tokens. proj [T, P] float32 (rows may be strided) holds q, k (heads x dim), v
+    (heads x vdim) and the raw gates (heads each) at the named columns; y [T, heads * vdim] float32; a request's memory
+    lives at ``state_off`` inside its slot of ``state`` [slots, n] float32."""
+    T = proj.shape[0]
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or y.shape != (T, heads * vdim) or dim > 1024 or \
+            state.shape[1] < state_off + matrix_memory_state_floats(heads, dim, vdim) or state.stride(1) != 1:
+        raise lib.KernelError("matrix_memory: shapes do not fit")
+    lib.call("tm_matrix_memory", proj.data_ptr(), proj.stride(0), q_col, k_col, v_col, i_col, f_col,
+             _opt(i_bias, "i_bias", torch.float32), _opt(f_bias, "f_bias", torch.float32), float(cap), float(q_scale),
+             _req(state, "state", torch.float32), state.stride(0), int(state_off), _req(cu_q, "cu_q", torch.int32),
+             _req(state_slots, "state_slots", torch.int32), _req(y, "y", torch.float32), int(n_seqs), heads, dim, vdim,
+             _stream())
+    return y

@@ -27,6 +27,9 @@ class Pending:
     table: torch.Tensor | None = None
     branch2: torch.Tensor | None = None      # a second branch output, and the multiplier of both (blocks whose
     scale: float = 1.0                        # branches read the same stream; norms that take them: RMSNorm32)
+    gate: torch.Tensor | None = None         # 32-bit pre-activations of a gate on the branch, and the gate's bias
+    gate_bias: torch.Tensor | None = None    # (norms that take them: GatedAddRMSNorm)
+    table_scale: float = 1.0                  # multiplier of the embedding rows (norms that read ``table``)
 
     @classmethod
     def of(cls, y: torch.Tensor) -> "Pending":
@@ -41,6 +44,10 @@ class Pending:
         kw = {"branch": self.branch, "partials": self.partials, "ids": self.ids, "table": self.table}
         if self.branch2 is not None or self.scale != 1.0:
             kw.update(branch2=self.branch2, scale=self.scale)
+        if self.gate is not None:
+            kw.update(gate=self.gate, gate_bias=self.gate_bias)
+        if self.table_scale != 1.0 and self.table is not None:
+            kw.update(table_scale=self.table_scale)
         return kw
 
 
@@ -116,5 +123,77 @@ class ParallelShiftBlock:
         return Pending(branch=mixed, branch2=fed, scale=self.mult)
 
 
+class ConvGatedBlock:
+    """Pre-norm block with two additions. Each sublayer reads its normed input h through a short causal convolution
+    over time, ``h + conv(h)`` with ``conv(h)_t = sum_j w[:, j] h_(t - taps + 1 + j)`` per channel (tensors ``canon1`` and
+    ``canon2`` of the layer, [width, taps]); and each sublayer's result enters the stream through a learned gate,
+    ``x <- x + sigmoid(W h + b) * sublayer(h + conv(h))`` (``rg1`` / ``rg1.b`` for the mixer, ``rg2`` / ``rg2.b`` for the
+    feed-forward), the gate reading h before the convolution. The last ``taps - 1`` inputs of both convolutions are
+    per-request state of the block ([2, taps - 1, width] in 32-bit), so a sequence may be cut anywhere. The gate's
+    product keeps its 32-bit accumulator; the norm that follows (``GatedAddRMSNorm``) applies the sigmoid and adds the
+    gated branch while it reads the row. The feed-forward may be absent."""
+
+    wants_run_context = True
+
+    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm, *, hidden_size: int, taps: int,
+                 names: dict[str, str] | None = None, dtype: torch.dtype, device: torch.device):
+        if not 1 <= taps <= 16:
+            raise ValueError(f"input convolutions of 1 to 16 taps are built, got {taps}")
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+        self.hidden_size, self.taps = hidden_size, int(taps)
+        self.dtype, self.device = dtype, device
+        self.names = {"conv1": "canon1", "conv2": "canon2", "gate1": "rg1", "gate1_bias": "rg1.b", "gate2": "rg2",
+                      "gate2_bias": "rg2.b", **(names or {})}
+        self.carry = (self.taps - 1) * hidden_size
+        self.w_conv: list = [None, None]
+        self.w_gate: list = [None, None]
+        self.b_gate: list = [None, None]
+
+    def _sides(self) -> list[int]:
+        return [1] if self.feed_forward is None else [1, 2]
+
+    def weight_specs(self):
+        from .spec import WeightSpec
+        H, n, out = self.hidden_size, self.names, []
+        for i in self._sides():
+            out += [WeightSpec(n[f"conv{i}"], (H, self.taps), dtype="float32", init=("normal", 0.2)),
+                    WeightSpec(n[f"gate{i}"], (H, H), init=("normal", 0.05)),
+                    WeightSpec(n[f"gate{i}_bias"], (H,), dtype="float32", init=("normal", 0.5))]
+        return out
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        for i in self._sides():
+            self.w_conv[i - 1] = tensors[self.names[f"conv{i}"]]
+            self.w_gate[i - 1] = tensors[self.names[f"gate{i}"]]
+            self.b_gate[i - 1] = tensors[self.names[f"gate{i}_bias"]]
+
+    def state_need(self):
+        from .spec import StateNeed
+        return StateNeed((2 * self.carry,), "float32") if self.taps > 1 else None
+
+    def _read(self, h: torch.Tensor, side: int, step: StepInputs, cache: LayerCache):
+        """(gate pre-activations [T, H] float32, h + conv(h)) of one sublayer."""
+        from ..kernels import ops
+        gate = ops.linear32(h, self.w_gate[side])
+        if self.taps == 1:          # one tap: conv(h) = w h, nothing is carried (the kernel never touches the state)
+            state = torch.empty((1, 0), dtype=torch.float32, device=h.device)
+        else:
+            state = cache.block_state[:, side * self.carry:(side + 1) * self.carry]
+        return gate, ops.canon_conv(h, self.w_conv[side], state, step.cu_q, step.seq_of_token, step.state_slots,
+                                    torch.empty_like(h))
+
+    def forward(self, resid: torch.Tensor, pending: Pending, step: StepInputs, cache: LayerCache) -> Pending:
+        h = self.mixer_norm.forward(resid, **pending.kwargs())
+        gate, hc = self._read(h, 0, step, cache)
+        out = Pending(branch=self.mixer.forward(hc, step, cache), gate=gate, gate_bias=self.b_gate[0])
+        if self.feed_forward is None:
+            return out
+        h = self.feed_forward_norm.forward(resid, **out.kwargs())
+        gate, hc = self._read(h, 1, step, cache)
+        return Pending(branch=self.feed_forward.forward(hc, step), gate=gate, gate_bias=self.b_gate[1])
+
+
+register_block("conv_gated", ConvGatedBlock)
 register_block("pre_norm", PreNormBlock)
 register_block("parallel_shift", ParallelShiftBlock)

@@ -52,6 +52,11 @@ class CacheLayout:
     def windows(self) -> list[int | None]:
         return [g.need.window for g in self.groups]
 
+    @property
+    def keep_first(self) -> list[int]:
+        """Per group: how many of a sequence's first positions stay readable behind a window."""
+        return [g.need.keep_first if g.need.window is not None else 0 for g in self.groups]
+
 
 def _build(role: str, spec: PartSpec | None, dtype: torch.dtype, device: torch.device):
     if spec is None:
@@ -113,10 +118,18 @@ class DecoderModel:
     # --- what the engine asks the parts -----------------------------------------------------------
 
     def parts(self) -> list:
-        """Every part of the model, layer by layer (mixer, feed-forward, the two norms), then the final norm."""
+        """Every part of the model, layer by layer (mixer, feed-forward, the two norms), then the final norm. A mixer
+        that is made of mixers is followed by them, so that each is asked for its step metadata and position limit."""
         out = []
+
+        def add(p):             # a part made of parts (``sub_parts()``) is followed by them
+            out.append(p)
+            for q in (p.sub_parts() if callable(getattr(p, "sub_parts", None)) else ()):
+                add(q)
         for blk in self.blocks:
-            out += [p for p in (blk.mixer, blk.feed_forward, blk.mixer_norm, blk.feed_forward_norm) if p is not None]
+            for p in (blk.mixer, blk.feed_forward, blk.mixer_norm, blk.feed_forward_norm):
+                if p is not None:
+                    add(p)
         return out + [self.final_norm]
 
     def max_positions(self) -> int:
@@ -182,7 +195,8 @@ class DecoderModel:
         s = self.spec
         parts = [p for blk in self.blocks for p in (blk, blk.mixer, blk.feed_forward, blk.mixer_norm, blk.feed_forward_norm)
                  if p is not None]
-        if self.dtype != torch.bfloat16 or not all(hasattr(p, "emit") for p in parts + [self.final_norm]):
+        if self.dtype != torch.bfloat16 or s.embedding_scale != 1.0 or \
+                not all(hasattr(p, "emit") for p in parts + [self.final_norm]):
             return None
         b = ProgramBuilder(self.device, self.dtype)
         try:
@@ -204,7 +218,7 @@ class DecoderModel:
         """Run the step's tokens; returns logits [n_want, vocab] float32."""
         s = self.spec
         resid = torch.empty((step.n_tokens, s.hidden_size), dtype=torch.float32, device=self.device)
-        pending = Pending(ids=step.token_ids, table=self.embedding)
+        pending = Pending(ids=step.token_ids, table=self.embedding, table_scale=s.embedding_scale)
         for pos, entry in enumerate(s.run_order):
             pending = self.blocks[entry.layer].forward(resid, pending, step, caches[pos])
         if step.n_want == 0:

@@ -92,5 +92,37 @@ class RMSNorm32:
         return (out, out2) if pair is not None else out
 
 
+class GatedAddRMSNorm:
+    """RMSNorm (32-bit products, plain weight, one rounding) over a stream that receives the previous branch through a
+    learned gate on the way: ``resid += sigmoid(gate + gate_bias) * branch``, the gate's pre-activations arriving as a
+    32-bit matrix product. Without a gate the branch is added as it is; at the start the stream is the embedding row
+    times ``table_scale`` (multiplied in 32-bit). Also a model's final norm (``rows``)."""
+
+    def __init__(self, *, hidden_size: int, eps: float, weight_name: str = "weight", dtype: torch.dtype,
+                 device: torch.device):
+        self.hidden_size, self.eps, self.weight_name = hidden_size, float(eps), weight_name
+        self.dtype, self.device = dtype, device
+        self.weight: torch.Tensor | None = None
+
+    def weight_specs(self) -> list[WeightSpec]:
+        return [WeightSpec(self.weight_name, (self.hidden_size,), dtype="float32", init=("ones_plus_normal", 0.1))]
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.weight_name]
+
+    def forward(self, resid: torch.Tensor, out: torch.Tensor | None = None, *, branch: torch.Tensor | None = None,
+                gate: torch.Tensor | None = None, gate_bias: torch.Tensor | None = None,
+                partials: torch.Tensor | None = None, ids: torch.Tensor | None = None, table: torch.Tensor | None = None,
+                table_scale: float = 1.0, rows: torch.Tensor | None = None) -> torch.Tensor:
+        if partials is not None:
+            raise NotImplementedError("the gated norm takes branch outputs, not partial products")
+        n = rows.numel() if rows is not None else resid.shape[0]
+        if out is None:
+            out = torch.empty((n, self.hidden_size), dtype=self.dtype, device=resid.device)
+        return ops.gated_add_rmsnorm(resid, self.weight, self.eps, out, branch=branch, gate=gate, gate_bias=gate_bias,
+                                     ids=ids, table=table, table_scale=table_scale, rows=rows)
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("rmsnorm_gated", GatedAddRMSNorm)
 register_norm("rmsnorm32", RMSNorm32)

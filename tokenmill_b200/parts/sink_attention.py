@@ -1,0 +1,145 @@
+"""Grouped-query attention with the options a windowed design may combine, each a constructor parameter:
+
+* key/query heads of ``head_dim`` and value heads of ``value_dim`` (they may differ);
+* an RMS norm over the WHOLE query projection and the whole key projection (all heads at once, plain weights), before
+  the rotation (``qk_norm``);
+* rotate-half rotation of the first ``rot_dims`` dimensions of each head, tables from a position-encoding part;
+* ``score = q . k * scale``, then ``softcap * tanh(score / softcap)`` (``softcap`` 0: none);
+* a sliding window that keeps the sequence's first tokens visible: position i sees j <= i when i - j < window or
+  j < keep_first (window 0: every key). Kept tokens keep their true positions;
+* a softmax with one added to the denominator, p_j = exp(s_j) / (1 + sum exp(s_j)): a sink of score 0 without a
+  value (``sink``);
+* a per-head output gate sigmoid(W_g h), one number per head, read from the same input as the projections
+  (``head_gate``).
+
+Projections q, k, v (and g) are held as one matrix whose product keeps its 32-bit accumulator; one kernel norms,
+rotates and writes the token's cache row ``[k | v]`` (a paged cache of one plane whose row holds all key heads, then
+all value heads); the attention kernel reads rows back through the block table, so a prompt portion sees its own keys.
+A mixer that runs beside others may be handed its columns of a shared product (``projection_weight`` /
+``forward_projected``).
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from ..registry import get_part, register_mixer
+from .base import LayerCache, StepInputs, StepMetadata, StepShape, part_limit_positions, part_max_positions
+from .spec import PagedKVNeed, PartSpec, StateNeed, WeightSpec
+
+
+class SinkWindowAttention:
+    def __init__(self, *, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, scale: float,
+                 position: PartSpec | None, rot_dims: int = 0, window: int | None = None, keep_first: int = 0,
+                 softcap: float = 0.0, sink: bool = True, qk_norm: bool = True, head_gate: bool = True, eps: float = 1e-6,
+                 names: dict[str, str] | None = None, dtype: torch.dtype, device: torch.device):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"heads ({num_heads}) must be a multiple of kv heads ({num_kv_heads})")
+        if value_dim > 256 or head_dim > 512:
+            raise ValueError("heads of up to 512 (keys) and 256 (values) are built")
+        self.hidden_size, self.nh, self.nkv, self.d, self.dv = hidden_size, num_heads, num_kv_heads, head_dim, value_dim
+        self.scale, self.softcap, self.eps = float(scale), float(softcap or 0.0), float(eps)
+        self.window, self.keep_first = int(window) if window else 0, int(keep_first or 0)
+        self.sink, self.qk_norm, self.head_gate = bool(sink), bool(qk_norm), bool(head_gate)
+        self.position = get_part("position", position.kind)(**position.params) if position is not None else None
+        self.rot_dims = int(rot_dims) if self.position is not None else 0
+        if self.rot_dims % 2 or self.rot_dims > head_dim:
+            raise ValueError(f"rot_dims ({self.rot_dims}) must be even and at most head_dim ({head_dim})")
+        self.dtype, self.device = dtype, device
+        self.names = {"q": "q", "k": "k", "v": "v", "q_norm": "q.norm", "k_norm": "k.norm", "g": "g", "o": "o",
+                      **(names or {})}
+        self.q_size, self.k_size, self.v_size = num_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * value_dim
+        self.proj_width = self.q_size + self.k_size + self.v_size + (num_heads if self.head_gate else 0)
+        self.w_in = self.w_o = self.g_q = self.g_k = self.cos = self.sin = None
+
+    # --- declarations -----------------------------------------------------------------------------------------
+
+    def weight_specs(self) -> list[WeightSpec]:
+        n, W = self.names, self.hidden_size
+        specs = [WeightSpec(n["q"], (self.q_size, W), init=("normal", 0.05)),
+                 WeightSpec(n["k"], (self.k_size, W), init=("normal", 0.05)),
+                 WeightSpec(n["v"], (self.v_size, W), init=("normal", 0.05))]
+        if self.qk_norm:
+            specs += [WeightSpec(n["q_norm"], (self.q_size,), dtype="float32", init=("ones_plus_normal", 0.1)),
+                      WeightSpec(n["k_norm"], (self.k_size,), dtype="float32", init=("ones_plus_normal", 0.1))]
+        if self.head_gate:
+            specs.append(WeightSpec(n["g"], (self.nh, W), init=("normal", 0.05)))
+        specs.append(WeightSpec(n["o"], (W, self.nh * self.dv), init=("normal", 0.05)))
+        return specs
+
+    def cache_need(self) -> PagedKVNeed:
+        return PagedKVNeed(1, self.k_size + self.v_size, self.window or None, planes=1,
+                           keep_first=self.keep_first if self.window else 0)
+
+    def state_need(self) -> StateNeed | None:
+        return None
+
+    def max_positions(self) -> int | None:
+        return part_max_positions(self.position) if self.position is not None else None
+
+    def limit_positions(self, n: int) -> None:
+        if self.position is not None:
+            part_limit_positions(self.position, n)
+
+    def activation_bytes(self, n_tokens: int) -> int:
+        elt = 4 if self.dtype == torch.float32 else 2
+        return n_tokens * (self.proj_width * 4 + (self.q_size + self.nh * self.dv + self.hidden_size) * elt + self.nh * 4)
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        n = self.names
+        rows = [tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]] + ([tensors[n["g"]]] if self.head_gate else [])
+        self.w_in = torch.cat(rows, dim=0).contiguous()
+        self.w_o = tensors[n["o"]]
+        if self.qk_norm:
+            self.g_q, self.g_k = tensors[n["q_norm"]], tensors[n["k_norm"]]
+        if self.position is not None:
+            self.cos, self.sin = self.position.tables(self.device)
+        else:       # no rotation: tables of no columns
+            self.cos = self.sin = torch.zeros((1, 0), dtype=torch.float32, device=self.device)
+
+    def projection_weight(self) -> torch.Tensor:
+        """[proj_width, hidden] rows [q; k; v; g]: what a shared product multiplies for this mixer."""
+        return self.w_in
+
+    # --- per-step work list -----------------------------------------------------------------------------------
+
+    def metadata_key(self):
+        return ("sink_attention", self.nh // self.nkv)
+
+    def step_metadata(self, shape: StepShape) -> StepMetadata:
+        """Row tiles of the attention kernel: 32 consecutive (token, head in group) rows of one request each."""
+        rows = ops.SINK_TILE_ROWS
+        per_seq = (shape.q_lens.astype(np.int64) * (self.nh // self.nkv) + rows - 1) // rows
+        tile_seq = np.repeat(np.arange(len(per_seq), dtype=np.int32), per_seq)
+        first = np.cumsum(per_seq) - per_seq
+        tile_row0 = ((np.arange(tile_seq.size) - np.repeat(first, per_seq)) * rows).astype(np.int32)
+        return StepMetadata({"tile_seq": tile_seq, "tile_row0": tile_row0}, {"n_tiles": int(tile_seq.size)},
+                            constant_in_graph=True)
+
+    # --- run --------------------------------------------------------------------------------------------------
+
+    def forward(self, x: torch.Tensor, step: StepInputs, cache: LayerCache) -> torch.Tensor:
+        return self.forward_projected(ops.linear32(x, self.w_in), step, cache)
+
+    def forward_projected(self, proj: torch.Tensor, step: StepInputs, cache: LayerCache) -> torch.Tensor:
+        """``proj`` [T, proj_width] float32 (a view of a wider product is fine): this mixer's columns [q | k | v | g]."""
+        T, dev = proj.shape[0], proj.device
+        q = torch.empty((T, self.q_size), dtype=self.dtype, device=dev)
+        gate = torch.empty((T, self.nh), dtype=torch.float32, device=dev) if self.head_gate else None
+        rows = cache.k.view(-1, self.k_size + self.v_size)
+        ops.qk_norm_rope_write(proj, heads=self.nh, kv_heads=self.nkv, dim=self.d, vdim=self.dv, rot_dims=self.rot_dims,
+                               wq=self.g_q, wk=self.g_k, eps=self.eps, positions=step.positions, cos=self.cos, sin=self.sin,
+                               slot_map=step.slot_maps[cache.group] if cache.writes else None, q_out=q,
+                               cache=rows if cache.writes else None, gate_out=gate)
+        meta = step.meta[self.metadata_key()]
+        heads = torch.empty((T, self.nh * self.dv), dtype=self.dtype, device=dev)
+        ops.sink_attention(q, cache.k, step.block_tables[cache.group], step.cu_q, step.kv_before, meta.arrays["tile_seq"],
+                           meta.arrays["tile_row0"], meta.host["n_tiles"], gate, heads, heads=self.nh, kv_heads=self.nkv,
+                           dim=self.d, vdim=self.dv, scale=self.scale, softcap=self.softcap, window=self.window,
+                           keep_first=self.keep_first, sink=self.sink)
+        return ops.linear(heads, self.w_o)
+
+
+register_mixer("sink_window_attention", SinkWindowAttention)

@@ -35,15 +35,18 @@ class PagedKVNeed:
     """A mixer that keeps per-token keys and values. window=None: all keys stay; window=w: a query at
     position p reads keys p-w+1..p only, and pages wholly behind every future window are given back.
     planes=2: a key row and a value row per token; planes=1: one row per token (a cache of latents, from
-    which keys and values are both derived)."""
+    which keys and values are both derived, or keys and values of different sizes side by side).
+    keep_first=n (with a window): the first n positions stay readable for every query, so their pages are never
+    given back."""
 
     kv_heads: int
     head_dim: int
     window: int | None = None
     planes: int = 2
+    keep_first: int = 0
 
     def group_key(self) -> tuple:
-        return ("paged_kv", self.kv_heads, self.head_dim, self.window, self.planes)
+        return ("paged_kv", self.kv_heads, self.head_dim, self.window, self.planes, self.keep_first)
 
 
 @dataclass(frozen=True)
@@ -106,6 +109,7 @@ class ModelSpec:
     max_positions: int
     eos_token_ids: list[int] = field(default_factory=list)
     ignored_name_patterns: tuple[str, ...] = ()   # checkpoint names that may be present and are not loaded
+    embedding_scale: float = 1.0                  # the stream starts as embedding row * this (multiplied in 32-bit)
 
     def validate(self) -> None:
         n = len(self.layers)

@@ -79,4 +79,39 @@ class SwiGLUFeedForward:
         return out
 
 
+class GatedFeedForward:
+    """Dense gated feed-forward ``down(act(gate(x)) * up(x))`` with the activation as a parameter: ``silu``, or
+    ``gelu_tanh``, 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))). No biases; gate and up are held as one matrix."""
+
+    def __init__(self, *, hidden_size: int, intermediate_size: int, activation: str = "silu",
+                 names: dict[str, str] | None = None, dtype: torch.dtype, device: torch.device):
+        if activation not in ops.GLU_ACTIVATIONS:
+            raise ValueError(f"activation must be one of {sorted(ops.GLU_ACTIVATIONS)}, got {activation!r}")
+        self.hidden_size, self.intermediate_size, self.activation = hidden_size, intermediate_size, activation
+        self.dtype, self.device = dtype, device
+        self.names = {"gate": "gate", "up": "up", "down": "down", **(names or {})}
+        self.w_gate_up = self.w_down = None
+
+    def weight_specs(self) -> list[WeightSpec]:
+        H, I, n = self.hidden_size, self.intermediate_size, self.names
+        return [WeightSpec(n["gate"], (I, H), init=("normal", 0.05)), WeightSpec(n["up"], (I, H), init=("normal", 0.05)),
+                WeightSpec(n["down"], (H, I), init=("normal", 0.05))]
+
+    def activation_bytes(self, n_tokens: int) -> int:
+        elt = 4 if self.dtype == torch.float32 else 2
+        return n_tokens * (3 * self.intermediate_size + self.hidden_size) * elt
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        n = self.names
+        self.w_gate_up = torch.cat([tensors[n["gate"]], tensors[n["up"]]], dim=0).contiguous()
+        self.w_down = tensors[n["down"]]
+
+    def forward(self, x: torch.Tensor, step: StepInputs | None = None) -> torch.Tensor:
+        gu = ops.linear(x, self.w_gate_up)
+        act = torch.empty((x.shape[0], self.intermediate_size), dtype=self.dtype, device=x.device)
+        ops.glu(gu, act, self.activation)
+        return ops.linear(act, self.w_down)
+
+
 register_feed_forward("swiglu", SwiGLUFeedForward)
+register_feed_forward("glu", GatedFeedForward)

@@ -140,12 +140,56 @@ def _kutirax_named(name: str) -> dict | None:
     return None
 
 
+def bobunex_attention(*, heads, kv_heads, dim, vdim, window, keep_first=0, scale=None, softcap=30.0, base=10000.0,
+                      rot_dims=None, scaling=None) -> dict:
+    """The ``mixer.left`` entry of a Bobunex layer; ``scaling`` = (factor, low, high, original) or None."""
+    rot = {"base": float(base), "dims": rot_dims if rot_dims is not None else dim}
+    if scaling is not None:
+        rot["scaling"] = dict(zip(("factor", "low", "high", "original"), scaling))
+    return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim,
+            "scale": float(scale if scale is not None else dim ** -0.5), "softcap": float(softcap),
+            "mask": {"size": window, "keep_first": keep_first}, "rot": rot}
+
+
+def bobunex_memory(*, heads, dim, vdim, gate_cap=15.0) -> dict:
+    """The ``mixer.right`` entry of a Bobunex layer."""
+    return {"heads": heads, "dim": dim, "vdim": vdim, "gate_cap": float(gate_cap)}
+
+
+def bobunex_config(*, vocab, width, layers, eps=1e-6, embedding_scale=1.0, taps=3) -> dict:
+    """config.json of a Bobunex model. ``layers``: (left entry, right entry, ff or None)."""
+    return {"architecture": "Bobunex", "vocab": vocab, "width": width, "norm": {"eps": eps},
+            "embedding": {"scale": float(embedding_scale)}, "canon": {"taps": taps},
+            "layers": [{"type": "parallel", "mixer": {"left": left, "right": right},
+                        "mlp": None if ff is None else {"kind": "dense", "ff": ff}} for left, right, ff in layers]}
+
+
+def _bobunex_named(name: str) -> dict | None:
+    A, M = bobunex_attention, bobunex_memory
+    if name == "bobunex-tiny-a":     # two windows (two cache groups), kept tokens inside one page, a layer without feed-forward
+        return bobunex_config(vocab=173, width=48, embedding_scale=5.0, taps=3, layers=[
+            (A(heads=6, kv_heads=3, dim=12, vdim=20, window=11, keep_first=3, scale=0.3, rot_dims=8, base=300.0,
+               scaling=(8.0, 1.0, 4.0, 64)), M(heads=3, dim=10, vdim=14, gate_cap=8.0), 56),
+            (A(heads=4, kv_heads=1, dim=16, vdim=8, window=37, keep_first=18, softcap=5.0, rot_dims=16), M(heads=2, dim=24, vdim=24), None)])
+    if name == "bobunex-tiny-b":     # two taps, every head its own keys, nothing kept, no frequency scaling, no cap on scores
+        return bobunex_config(vocab=300, width=80, eps=1e-5, embedding_scale=1.0, taps=2, layers=[
+            (A(heads=5, kv_heads=5, dim=8, vdim=8, window=33, keep_first=0, softcap=0.0, rot_dims=4, base=500000.0),
+             M(heads=4, dim=20, vdim=20, gate_cap=15.0), 100)] * 2)
+    if name == "bobunex-tiny-c":     # five taps, one key head, a window longer than most prompts, wide memory columns, rotation switched off
+        return bobunex_config(vocab=130, width=56, eps=1e-5, embedding_scale=0.5, taps=5, layers=[
+            (A(heads=7, kv_heads=1, dim=10, vdim=36, window=300, keep_first=40, rot_dims=0), M(heads=1, dim=40, vdim=72, gate_cap=3.0), 40),
+            (A(heads=2, kv_heads=2, dim=34, vdim=10, window=5, keep_first=1, rot_dims=34, scaling=(4.0, 1.0, 2.0, 16)),
+             M(heads=5, dim=6, vdim=9, gate_cap=30.0), 24)])
+    return None
+
+
 def named_config(name: str) -> dict:
-    cfg = _kutirax_named(name.lower())
+    cfg = _kutirax_named(name.lower()) or _bobunex_named(name.lower())
     if cfg is not None:
         return cfg
     try:
         return qwen2_config(**NAMED_SIZES[name.lower()])
     except KeyError:
-        known = sorted(NAMED_SIZES) + ["kutirax-tiny-a", "kutirax-tiny-b", "kutirax-tiny-c"]
+        known = sorted(NAMED_SIZES) + ["kutirax-tiny-a", "kutirax-tiny-b", "kutirax-tiny-c", "bobunex-tiny-a", "bobunex-tiny-b",
+                                       "bobunex-tiny-c"]
         raise ValueError(f"unknown size name {name!r}; known: {known}") from None
