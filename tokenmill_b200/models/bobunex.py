@@ -19,7 +19,7 @@ from ..registry import register_architecture
 def bobunex_spec(cfg: BobunexConfig) -> ModelSpec:
     d = cfg.width
     norm = PartSpec("rmsnorm_gated", {"hidden_size": d, "eps": cfg.eps, "weight_name": ""})
-    layers = []
+    layers, unused = [], []
     for i, layer in enumerate(cfg.layers):
         a, r = layer.mixer["left"], layer.mixer["right"]
         rope = None
@@ -39,6 +39,8 @@ def bobunex_spec(cfg: BobunexConfig) -> ModelSpec:
         ffn = None
         if layer.mlp is not None:
             ffn = PartSpec("glu", {"hidden_size": d, "intermediate_size": layer.mlp["ff"], "activation": "gelu_tanh"})
+        if ffn is None:     # a file may still carry the absent sublayer's norm, convolution and gate: they are not loaded
+            unused += [f"l{i}.norm2", f"l{i}.canon2", f"l{i}.rg2", f"l{i}.mlp."]
         layers.append(LayerSpec(prefix=f"l{i}", block="conv_gated", mixer=mixer, feed_forward=ffn, mixer_norm=norm,
                                 feed_forward_norm=norm if ffn is not None else None, mixer_name="mix",
                                 feed_forward_name="mlp", mixer_norm_name="norm1", feed_forward_norm_name="norm2",
@@ -46,7 +48,8 @@ def bobunex_spec(cfg: BobunexConfig) -> ModelSpec:
     return ModelSpec(architecture=cfg.architecture, hidden_size=d, vocab_size=cfg.vocab, embedding_name="embed",
                      layers=layers, run_order=[RunEntry(i) for i in range(len(layers))], final_norm=norm,
                      final_norm_prefix="final.norm", lm_head_name="head", max_positions=cfg.max_positions,
-                     eos_token_ids=list(cfg.eos_token_ids), embedding_scale=cfg.embedding_scale)
+                     eos_token_ids=list(cfg.eos_token_ids), embedding_scale=cfg.embedding_scale,
+                     ignored_name_patterns=tuple(unused))
 
 
 register_architecture("Bobunex", BobunexConfig.from_dict, bobunex_spec)
