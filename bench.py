@@ -27,8 +27,8 @@ chunked prefill with a 2,048-token budget; ``7b-prefix``: Qwen2.5-7B sizes, cont
 4,096-token prompts that share their first 1,024 tokens, 512 new tokens, prefix caching, a pool too small for
 all of them so that requests are preempted.
 
-``--design kutirax [--design-sizes s|m] [--kernels]`` measures the Kutirax design (latent attention with a window,
-state-space layers, experts) beside Qwen2 at the same width, depth and vocabulary: one 2,048-token prompt and decode
+``--design kutirax|bobunex [--design-sizes s|m] [--kernels]`` measures another design (Kutirax: latent attention with a window,
+state-space layers, experts; Bobunex: windowed attention with a sink beside a matrix memory) beside Qwen2 at the same width, depth and vocabulary: one 2,048-token prompt and decode
 steps of 8 and 32 requests, and with ``--kernels`` the device time by kernel name of one step of each kind.
 
 The engine runs on one GPU: for --gpus N > 1 a line says so and the exit code is 2.
@@ -720,29 +720,42 @@ DESIGN_SIZES = {
               latent=dict(heads=8, dim=64, rot_dim=32, vdim=64, q_rank=384, kv_rank=256, window=512),
               mamba=dict(heads=32, vdim=64, state=64, groups=4, conv=4, norm_groups=4),
               dense=4096, moe=(16, 2, 1024),
+              bobunex=dict(left=dict(heads=8, kv_heads=2, dim=128, vdim=64, window=512, keep_first=64, rot_dims=64,
+                                     softcap=50.0, base=500000.0, scaling=(8.0, 1.0, 4.0, 8192)),
+                           right=dict(heads=8, dim=64, vdim=128), ff=2816, taps=4),
               qwen=dict(num_attention_heads=8, num_key_value_heads=2, head_dim=128, intermediate_size=2816)),
     "m": dict(width=2048,
               latent=dict(heads=16, dim=128, rot_dim=64, vdim=128, q_rank=768, kv_rank=512, window=1024),
               mamba=dict(heads=64, vdim=64, state=128, groups=8, conv=4, norm_groups=8),
               dense=8192, moe=(32, 4, 1024),
+              bobunex=dict(left=dict(heads=16, kv_heads=2, dim=128, vdim=128, window=1024, keep_first=128, rot_dims=64,
+                                     softcap=50.0, base=500000.0, scaling=(8.0, 1.0, 4.0, 8192)),
+                           right=dict(heads=16, dim=128, vdim=128), ff=5632, taps=4),
               qwen=dict(num_attention_heads=16, num_key_value_heads=2, head_dim=128, intermediate_size=5632)),
 }
 
 
-def design_model_dirs(size: str, vocab: int):
-    """(Kutirax folder, Qwen2 folder, description): four layers each, random weights, the same width and vocabulary.
-    Kutirax: state-space + dense, latent attention + experts (twice), state-space + experts."""
+def design_model_dirs(size: str, vocab: int, design: str = "kutirax"):
+    """(the design's folder, Qwen2 folder, description): four layers each, random weights, the same width and vocabulary.
+    Kutirax: state-space + dense, latent attention + experts (twice), state-space + experts. Bobunex: four layers of
+    windowed attention beside a matrix memory, with a gated gelu feed-forward."""
     from tokenmill_b200.weights import qwen2_config, write_random_model
-    from tokenmill_b200.weights.random_init import kutirax_config, kutirax_latent, kutirax_mamba
+    from tokenmill_b200.weights.random_init import (bobunex_attention, bobunex_config, bobunex_memory, kutirax_config,
+                                                    kutirax_latent, kutirax_mamba)
     z = DESIGN_SIZES[size]
-    lat, mam, moe = kutirax_latent(**z["latent"]), kutirax_mamba(**z["mamba"]), ("moe", *z["moe"])
-    kcfg = kutirax_config(vocab=vocab, width=z["width"], eps=1e-5, residual_mult=0.5, layers=[
-        ("mamba2", mam, ("dense", z["dense"])), ("latent_attention", lat, moe), ("latent_attention", lat, moe),
-        ("mamba2", mam, moe)])
+    if design == "bobunex":
+        b = z["bobunex"]
+        kcfg = bobunex_config(vocab=vocab, width=z["width"], eps=1e-6, embedding_scale=8.0, taps=b["taps"], layers=[
+            (bobunex_attention(**b["left"]), bobunex_memory(**b["right"]), b["ff"])] * 4)
+    else:
+        lat, mam, moe = kutirax_latent(**z["latent"]), kutirax_mamba(**z["mamba"]), ("moe", *z["moe"])
+        kcfg = kutirax_config(vocab=vocab, width=z["width"], eps=1e-5, residual_mult=0.5, layers=[
+            ("mamba2", mam, ("dense", z["dense"])), ("latent_attention", lat, moe), ("latent_attention", lat, moe),
+            ("mamba2", mam, moe)])
     qcfg = qwen2_config(vocab_size=vocab, hidden_size=z["width"], num_hidden_layers=4, rope_theta=1000000.0,
                         rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=32768, **z["qwen"])
     dirs = []
-    for name, cfg in (("kutirax", kcfg), ("qwen2", qcfg)):
+    for name, cfg in ((design, kcfg), ("qwen2", qcfg)):
         tmp = tempfile.TemporaryDirectory(prefix=f"tokenmill_bench_{name}_")
         t0 = time.time()
         write_random_model(tmp.name, cfg, seed=0)
@@ -791,20 +804,20 @@ def kernel_table(engine, tokens: int, batch: int) -> dict:
 
 
 def run_design(args) -> dict:
-    """Prompt and decode throughput of Kutirax beside Qwen2 at the same width, depth and vocabulary (random weights):
+    """Prompt and decode throughput of another design (Kutirax, Bobunex) beside Qwen2 at the same width, depth and vocabulary (random weights):
     one 2,048-token prompt; decode steps of 8 and of 32 requests behind 512-token prompts, in captured graphs."""
     import torch
     from tokenmill_b200 import EngineConfig
     from tokenmill_b200.engine import LLMEngine
     global NEW_TOKENS
     vocab = SIZES["vocab_size"]
-    kdir, qdir, z = design_model_dirs(args.design_sizes, vocab)
-    result = {"design": "Kutirax", "beside": "Qwen2", "sizes": args.design_sizes, "width": z["width"], "layers": 4,
+    kdir, qdir, z = design_model_dirs(args.design_sizes, vocab, args.design)
+    result = {"design": args.design.capitalize(), "beside": "Qwen2", "sizes": args.design_sizes, "width": z["width"], "layers": 4,
               "dtype": "bfloat16", "data": "synthetic", "prefill_tokens": args.prefill_tokens, "points": {}}
     sampler = ClockSampler()
     sampler.start()
     try:
-        for name, folder in (("kutirax", kdir.name), ("qwen2", qdir.name)):
+        for name, folder in ((args.design, kdir.name), ("qwen2", qdir.name)):
             cfg = EngineConfig(model=folder, dtype="bfloat16", block_size=PAGE, max_model_len=4096, max_num_seqs=64,
                                max_num_batched_tokens=4096, kv_cache_mb=3072, watermark=0.0, cuda_graphs=not args.no_graphs,
                                cuda_graph_max_batch=64)
@@ -844,7 +857,7 @@ def main() -> int:
                     help="profiling aid with --only decode_b<batch>: prompts of this many tokens instead of 512")
     ap.add_argument("--no-skip", action="store_true", help="profiling aid: time the decode steps right behind the prompt")
     ap.add_argument("--no-fp32", action="store_true", help="leave out the float32 engine's points")
-    ap.add_argument("--design", default="", choices=["", "kutirax"],
+    ap.add_argument("--design", default="", choices=["", "kutirax", "bobunex"],
                     help="measure another design beside Qwen2 at equal width and depth instead of the headline bench")
     ap.add_argument("--design-sizes", default="s", choices=sorted(DESIGN_SIZES), help="with --design: which layer sizes")
     ap.add_argument("--kernels", action="store_true", help="with --design: add device time by kernel name (profiler)")

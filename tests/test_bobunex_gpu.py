@@ -29,7 +29,7 @@ from replay_util import (check_against_plain, make_requests, mixed_steps, portio
 
 pytestmark = pytest.mark.gpu
 
-SIZES = ["bobunex-tiny-a", "bobunex-tiny-b", "bobunex-tiny-c"]
+SIZES = ["bobunex-tiny-a", "bobunex-tiny-b", "bobunex-tiny-c", "bobunex-tiny-d"]
 LENGTHS = [70, 133, 45, 200, 96, 61]
 DEV = "cuda:0"
 
@@ -211,7 +211,7 @@ def test_rotary_frequencies_with_wavelength_scaling():
     assert (cos.double() - ang.cos()).abs().max() < 1e-7 and (sin.double() - ang.sin()).abs().max() < 1e-7
 
 
-def _attend(dtype, H, G, d, dv, rot_dims, window, keep_first, softcap, sink, q_lens, starts, page=8, sharpen=None):
+def _attend(dtype, H, G, d, dv, rot_dims, window, keep_first, softcap, sink, q_lens, starts, page=8, sharpen=None, tc=False, hot=None):
     """Kernel pair (norm + rotation + cache write, attention) over a paged cache filled step by step, against the plain
     attention over whole sequences. Returns (engine output, plain output) for the LAST step's rows."""
     from tokenmill_b200.kernels import ops
@@ -221,10 +221,15 @@ def _attend(dtype, H, G, d, dv, rot_dims, window, keep_first, softcap, sink, q_l
     total = [s + q for s, q in zip(starts, q_lens)]
     P = H * d + G * d + G * dv + H
     proj = [torch.randn(t, P) for t in total]
-    if sharpen is not None:
-        for p in proj:
-            p[:, :H * d] *= sharpen
     wq, wk = 1 + 0.1 * torch.randn(H * d), 1 + 0.1 * torch.randn(G * d)
+    if sharpen is not None:             # (the norm undoes a scaling of q itself: scale its weight)
+        wq = wq * sharpen
+    if hot is not None:                 # all scores equal; a few keys carry large values, so that seeing one shows
+        for p in proj:
+            p[:, :H * d] = 0.0
+            for j in hot:
+                if j < p.shape[0]:
+                    p[j, H * d + G * d:H * d + G * d + G * dv] *= 60.0
     rope = RotaryEmbedding(head_dim=max(rot_dims, 2), theta=100.0, max_positions=max(total) + 1, precise=True)
     cos, sin = rope.tables(torch.device(DEV))
     if rot_dims == 0:
@@ -258,14 +263,16 @@ def _attend(dtype, H, G, d, dv, rot_dims, window, keep_first, softcap, sink, q_l
                                cache=cache.view(-1, G * (d + dv)), gate_out=gate)
         if phase == 1:
             Gq = H // G
-            per = [-(-n * Gq // 32) for n in lens]
+            tile = 64 if tc else 32
+            per = [-(-n * Gq // tile) for n in lens]
             tile_seq = np.repeat(np.arange(n_seq), per)
-            tile_row0 = np.concatenate([np.arange(n) * 32 for n in per])
+            tile_row0 = np.concatenate([np.arange(n) * tile for n in per])
             cu = np.zeros(n_seq + 1, dtype=np.int32)
             cu[1:] = np.cumsum(lens)
             outs = ops.sink_attention(q, cache, bt, _t(cu), _t(befores), _t(tile_seq), _t(tile_row0), int(tile_seq.size), gate,
                                       torch.empty(T, H * dv, dtype=dtype, device=DEV), heads=H, kv_heads=G, dim=d, vdim=dv,
-                                      scale=0.3, softcap=softcap, window=window, keep_first=keep_first, sink=sink)
+                                      scale=0.3, softcap=softcap, window=window, keep_first=keep_first, sink=sink,
+                                      tensor_cores=tc)
     ref = []
     freqs = pb.rotary_frequencies(rot_dims, 100.0, None) if rot_dims else None
     for s in range(n_seq):
@@ -314,6 +321,40 @@ def test_attention_kernels_prompt_portion_and_decoding(dtype, case):
     tol = 2e-5 if dtype == torch.float32 else 3e-2
     got, ref = _attend(dtype, q_lens=[50, 23, 1, 1], starts=[0, 61, 40, 95], **case)
     assert (got - ref).abs().max() < tol * max(1.0, float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("case", [
+    dict(H=4, G=2, d=32, dv=64, rot_dims=8, window=70, keep_first=20, softcap=4.0, sink=True),
+    dict(H=6, G=1, d=64, dv=32, rot_dims=64, window=13, keep_first=130, softcap=0.0, sink=True),
+    dict(H=2, G=2, d=128, dv=128, rot_dims=0, window=0, keep_first=0, softcap=30.0, sink=False),
+    dict(H=8, G=2, d=64, dv=128, rot_dims=16, window=100, keep_first=1, softcap=50.0, sink=True),
+])
+def test_tensor_core_attention_kernel(case):
+    """The mma.sync kernel on the same mixed step (a 200-token prompt so that kept blocks, skipped blocks and window
+    blocks all occur; a portion behind 150 cached tokens; single tokens), against the plain attention on the rounded
+    q, k, v; and against the CUDA-core kernel."""
+    q_lens, starts = [200, 23, 1, 1], [0, 150, 40, 333]
+    got, ref = _attend(torch.bfloat16, q_lens=q_lens, starts=starts, tc=True, **case)
+    assert (got - ref).abs().max() < 3e-2 * max(1.0, float(ref.abs().max()))
+    slow, _ = _attend(torch.bfloat16, q_lens=q_lens, starts=starts, tc=False, **case)
+    assert (got - slow).abs().max() < 3e-2 * max(1.0, float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("tc", [False, True])
+def test_attention_window_edges_with_hot_keys(tc):
+    """All scores equal and a few keys with values sixty times the others': a row that sees such a key one position
+    too early or too late is off by far more than rounding. Hot keys sit where rows of the step have their window's
+    first key, the key before it, the last kept token and the one behind it, and at the borders of the kernels' key
+    blocks (31, 32, 63, 64, 128), in a prompt and in decoded tokens."""
+    case = dict(H=4, G=2, d=64, dv=32, rot_dims=8, softcap=30.0, sink=True)
+    hot = [5, 6, 31, 32, 63, 64, 100, 128, 129, 140]
+    kw = dict(q_lens=[230, 1, 1, 1], starts=[0, 133, 134, 209], hot=hot, tc=tc, **case)
+    got, ref = _attend(torch.bfloat16, window=70, keep_first=6, **kw)
+    assert (got - ref).abs().max() < 3e-2 * float(ref.abs().max())
+    for dw, dk in ((1, 0), (-1, 0), (0, 1), (0, -1)):
+        _, other = _attend(torch.bfloat16, window=70 + dw, keep_first=6 + dk, **kw)
+        rows = (other - ref).abs().amax(dim=1) > 6e-2 * float(ref.abs().max())
+        assert int(rows[:230].sum()) >= 5 and (dk != 0 or bool(rows[230:].any())), (dw, dk)
 
 
 def test_window_and_kept_edges_with_sharp_queries():

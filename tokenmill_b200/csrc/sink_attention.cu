@@ -148,17 +148,16 @@ __global__ void __launch_bounds__(kSinkWarps * 32) sink_attention_kernel(
       continue;
     }
     __syncthreads();
-    for (int idx = tid; idx < kSinkKeyTile * (d + dv); idx += blockDim.x) {
-      const int jj = idx / (d + dv), e = idx - jj * (d + dv);
+    {   // eight threads a key row: one page lookup each, then loads that do not wait on one another
+      const int jj = tid >> 3, part = tid & 7;
       const int j = kt + jj;
-      float v = 0.f;
-      if (j <= j_hi && (j >= j_lo || j < keep_first)) {
-        const int page = table[j / page_size];
-        const T* src = cache + ((size_t)page * page_size + (j % page_size)) * row_width;
-        v = e < d ? to_float(src[kvh * d + e]) : to_float(src[v_off + kvh * dv + (e - d)]);
-      }
-      if (e < d) ks[jj * KS + e] = v;
-      else vs[jj * dv + (e - d)] = v;
+      const bool seen = j <= j_hi && (j >= j_lo || j < keep_first);
+      const T* src = cache;
+      if (seen) src += ((size_t)table[j / page_size] * page_size + (j % page_size)) * row_width;
+      const T* kp = src + kvh * d;
+      const T* vp = src + v_off + kvh * dv;
+      for (int e = part; e < d; e += 8) ks[jj * KS + e] = seen ? to_float(kp[e]) : 0.f;
+      for (int e = part; e < dv; e += 8) vs[jj * dv + e] = seen ? to_float(vp[e]) : 0.f;
     }
     __syncthreads();
     if (warp_idle) continue;

@@ -44,7 +44,7 @@ def find_nvcc() -> str:
 
 # Files of the ``hybrid`` and ``gated`` libraries; ``main`` is every other .cu file. SHARED files are compiled into all.
 HYBRID = ("norm_pair.cu", "latent_attention.cu", "latent_attention_mma_bf16.cu", "ssm_scan.cu", "routed_ffn.cu")
-GATED = ("gated_block.cu", "sink_attention.cu", "matrix_memory.cu")
+GATED = ("gated_block.cu", "sink_attention.cu", "sink_attention_mma_bf16.cu", "matrix_memory.cu")
 SHARED = ("gemm_f32.cu",)
 GROUPS = ("main", "hybrid", "gated")
 _PREFIX = {"main": "libtokenmill_kernels_", "hybrid": "libtokenmill_hybrid_", "gated": "libtokenmill_gated_"}

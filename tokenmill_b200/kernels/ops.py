@@ -1132,18 +1132,34 @@ def qk_norm_rope_write(proj: torch.Tensor, *, heads: int, kv_heads: int, dim: in
 
 
 SINK_TILE_ROWS = 32
+SINK_TC_TILE_ROWS = 64
+
+
+def sink_attention_tc_ok(dtype: torch.dtype, dim: int, vdim: int) -> bool:
+    """Whether the tensor-core kernel takes these shapes (bfloat16, key and value heads of 32, 64 or 128 each)."""
+    return dtype == torch.bfloat16 and dim in (32, 64, 128) and vdim in (32, 64, 128) and \
+        os.environ.get("TOKENMILL_SINK_TC", "1") != "0"
 
 
 def sink_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, cu_q: torch.Tensor,
                    kv_before: torch.Tensor, tile_seq: torch.Tensor, tile_row0: torch.Tensor, n_tiles: int,
                    gate: torch.Tensor | None, out: torch.Tensor, *, heads: int, kv_heads: int, dim: int, vdim: int,
-                   scale: float, softcap: float, window: int, keep_first: int, sink: bool) -> torch.Tensor:
-    """q [T, H d]; cache [pages, page_size, 1, G d + G dv]; tiles of 32 (token, head in group) rows of one request;
-    gate [T, H] float32 or None; out [T, H dv]."""
+                   scale: float, softcap: float, window: int, keep_first: int, sink: bool,
+                   tensor_cores: bool = False) -> torch.Tensor:
+    """q [T, H d]; cache [pages, page_size, 1, G d + G dv]; tiles of 32 (``tensor_cores``: 64) (token, head in group)
+    rows of one request; gate [T, H] float32 or None; out [T, H dv]."""
     T = q.shape[0]
     row = kv_heads * (dim + vdim)
     if cache.shape[-1] != row or q.shape != (T, heads * dim) or out.shape != (T, heads * vdim):
         raise lib.KernelError("sink_attention: shapes do not fit")
+    if tensor_cores:
+        lib.call("tm_sink_attention_mma_bf16", _req(q, "q", torch.bfloat16), _req(cache, "cache", torch.bfloat16), row,
+                 kv_heads * dim, _req(block_table, "block_table", torch.int32), block_table.stride(0),
+                 _req(cu_q, "cu_q", torch.int32), _req(kv_before, "kv_before", torch.int32),
+                 _req(tile_seq, "tile_seq", torch.int32), _req(tile_row0, "tile_row0", torch.int32), int(n_tiles),
+                 _opt(gate, "gate", torch.float32), _req(out, "out", torch.bfloat16), heads, kv_heads, dim, vdim,
+                 cache.shape[1], float(scale), float(softcap), int(window), int(keep_first), int(bool(sink)), _stream())
+        return out
     lib.call("tm_sink_attention", _code(q.dtype), _req(q, "q"), _req(cache, "cache", q.dtype), row, kv_heads * dim,
              _req(block_table, "block_table", torch.int32), block_table.stride(0), _req(cu_q, "cu_q", torch.int32),
              _req(kv_before, "kv_before", torch.int32), _req(tile_seq, "tile_seq", torch.int32),

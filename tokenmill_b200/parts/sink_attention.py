@@ -52,6 +52,10 @@ class SinkWindowAttention:
                       **(names or {})}
         self.q_size, self.k_size, self.v_size = num_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * value_dim
         self.proj_width = self.q_size + self.k_size + self.v_size + (num_heads if self.head_gate else 0)
+        # bfloat16 with key and value heads of 32, 64 or 128: tensor cores, 64 rows a tile; anything else (and the 32-bit
+        # path): the shape-generic kernel on CUDA cores, 32 rows a tile
+        self.tensor_cores = ops.sink_attention_tc_ok(dtype, head_dim, value_dim)
+        self.tile_rows = ops.SINK_TC_TILE_ROWS if self.tensor_cores else ops.SINK_TILE_ROWS
         self.w_in = self.w_o = self.g_q = self.g_k = self.cos = self.sin = None
 
     # --- declarations -----------------------------------------------------------------------------------------
@@ -106,11 +110,11 @@ class SinkWindowAttention:
     # --- per-step work list -----------------------------------------------------------------------------------
 
     def metadata_key(self):
-        return ("sink_attention", self.nh // self.nkv)
+        return ("sink_attention", self.nh // self.nkv, self.tile_rows)
 
     def step_metadata(self, shape: StepShape) -> StepMetadata:
-        """Row tiles of the attention kernel: 32 consecutive (token, head in group) rows of one request each."""
-        rows = ops.SINK_TILE_ROWS
+        """Row tiles of the attention kernel: ``tile_rows`` consecutive (token, head in group) rows of one request each."""
+        rows = self.tile_rows
         per_seq = (shape.q_lens.astype(np.int64) * (self.nh // self.nkv) + rows - 1) // rows
         tile_seq = np.repeat(np.arange(len(per_seq), dtype=np.int32), per_seq)
         first = np.cumsum(per_seq) - per_seq
@@ -138,7 +142,7 @@ class SinkWindowAttention:
         ops.sink_attention(q, cache.k, step.block_tables[cache.group], step.cu_q, step.kv_before, meta.arrays["tile_seq"],
                            meta.arrays["tile_row0"], meta.host["n_tiles"], gate, heads, heads=self.nh, kv_heads=self.nkv,
                            dim=self.d, vdim=self.dv, scale=self.scale, softcap=self.softcap, window=self.window,
-                           keep_first=self.keep_first, sink=self.sink)
+                           keep_first=self.keep_first, sink=self.sink, tensor_cores=self.tensor_cores)
         return ops.linear(heads, self.w_o)
 
 

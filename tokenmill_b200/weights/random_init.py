@@ -180,6 +180,11 @@ def _bobunex_named(name: str) -> dict | None:
             (A(heads=7, kv_heads=1, dim=10, vdim=36, window=300, keep_first=40, rot_dims=0), M(heads=1, dim=40, vdim=72, gate_cap=3.0), 40),
             (A(heads=2, kv_heads=2, dim=34, vdim=10, window=5, keep_first=1, rot_dims=34, scaling=(4.0, 1.0, 2.0, 16)),
              M(heads=5, dim=6, vdim=9, gate_cap=30.0), 24)])
+    if name == "bobunex-tiny-d":     # head sizes the tensor-core attention takes (bfloat16): 32 | 64 and 64 | 32, kept tokens across pages
+        return bobunex_config(vocab=210, width=64, eps=1e-6, embedding_scale=3.0, taps=4, layers=[
+            (A(heads=4, kv_heads=2, dim=32, vdim=64, window=70, keep_first=20, scale=0.2, rot_dims=16, scaling=(4.0, 1.0, 4.0, 128)),
+             M(heads=2, dim=16, vdim=32, gate_cap=10.0), 96),
+            (A(heads=3, kv_heads=1, dim=64, vdim=32, window=20, keep_first=5, softcap=8.0, rot_dims=64), M(heads=4, dim=8, vdim=8), 48)])
     return None
 
 
@@ -191,5 +196,5 @@ def named_config(name: str) -> dict:
         return qwen2_config(**NAMED_SIZES[name.lower()])
     except KeyError:
         known = sorted(NAMED_SIZES) + ["kutirax-tiny-a", "kutirax-tiny-b", "kutirax-tiny-c", "bobunex-tiny-a", "bobunex-tiny-b",
-                                       "bobunex-tiny-c"]
+                                       "bobunex-tiny-c", "bobunex-tiny-d"]
         raise ValueError(f"unknown size name {name!r}; known: {known}") from None
