@@ -404,6 +404,39 @@ def test_matrix_memory_kernel_under_cuts(heads, d, dv):
     assert float(state[0].abs().max()) == 0.0 and float(state[:, :8].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("heads,d,dv,slice_len", [(3, 10, 14, 8), (2, 64, 40, 16), (1, 260, 24, 5)])
+def test_matrix_memory_over_time_slices(heads, d, dv, slice_len):
+    """Three passes over time slices against the walk in one piece, from a state that an earlier step left: three
+    requests of 61, 1 and 16 tokens (last slices that are not full, a request of one slice, one that fills its slices
+    exactly); outputs and the states left behind agree to rounding."""
+    from tokenmill_b200.kernels import ops
+    torch.manual_seed(5)
+    P = 2 * heads * d + heads * dv + 2 * heads
+    col = dict(q_col=0, k_col=heads * d, v_col=2 * heads * d, i_col=2 * heads * d + heads * dv,
+               f_col=2 * heads * d + heads * dv + heads)
+    floats = ops.matrix_memory_state_floats(heads, d, dv)
+    bi, bf = torch.randn(heads, device=DEV), torch.randn(heads, device=DEV) + 2
+    kw = dict(i_bias=bi, f_bias=bf, cap=6.0, q_scale=d ** -0.5, state_off=0, n_seqs=3, heads=heads, dim=d, vdim=dv, **col)
+    warm, rows = torch.randn(9, P, device=DEV), torch.randn(78, P, device=DEV)
+    results = []
+    for sliced in (False, True):
+        state = torch.zeros(5, floats, device=DEV)
+        cu, _, slots = _step_arrays([3, 3, 3], [4, 0, 2])
+        ops.matrix_memory(warm, state=state, cu_q=cu, state_slots=slots, y=torch.empty(9, heads * dv, device=DEV), **kw)
+        cu, _, slots = _step_arrays([61, 1, 16], [4, 0, 2])
+        y = torch.empty(78, heads * dv, device=DEV)
+        extra = {}
+        if sliced:
+            n = ops.matrix_memory_slice_records(78, 3, slice_len)
+            extra = dict(slice_len=slice_len, slices=torch.full((n * floats,), float("nan"), device=DEV))
+        ops.matrix_memory(rows, state=state, cu_q=cu, state_slots=slots, y=y, **kw, **extra)
+        results.append((y.cpu(), state.cpu()))
+    (y0, s0), (y1, s1) = results
+    assert (y0 - y1).abs().max() < 2e-5 * max(1.0, float(y0.abs().max()))
+    assert (s0 - s1).abs().max() < 2e-5 * max(1.0, float(s0.abs().max()))
+    assert float(s1[1].abs().max()) == 0.0 and float(s1[3].abs().max()) == 0.0
+
+
 # --- the whole model under every cut ----------------------------------------------------------------------------
 
 @pytest.mark.parametrize("size", SIZES)
@@ -511,6 +544,23 @@ def test_a_far_key_and_an_old_state_show(bobunex_dirs, tmp_path):
             else mixed_steps(reqs, seed=3)
         outputs = run_trace(folder, "float32", steps, max_tokens, tmp_path / mode)
         check_against_plain(steps, outputs, reqs, plain, "float32")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_time_sliced_memory_under_every_cut(bobunex_dirs, plain_memo, dtype, tmp_path, monkeypatch):
+    """The three-pass recurrence switched on for portions from 12 tokens with slices of 8: whole prompts, portions and
+    mixed batches (requests of one token beside requests of many slices) against the plain recurrence."""
+    from tokenmill_b200.parts import matrix_memory
+    monkeypatch.setattr(matrix_memory, "SLICED_FROM", 12)
+    monkeypatch.setattr(matrix_memory, "SLICE_LEN", 8)
+    for size in ("bobunex-tiny-a", "bobunex-tiny-c"):
+        folder = bobunex_dirs[size]
+        vocab = json.loads((folder / "config.json").read_text())["vocab"]
+        reqs = make_requests(vocab, LENGTHS, seed=11)
+        for mode in ("whole", "portions", "mixed"):
+            steps, max_tokens = _steps(mode, reqs)
+            outputs = run_trace(folder, dtype, steps, max_tokens, tmp_path / f"{size}_{mode}")
+            _check(steps, outputs, reqs, _plain(folder, reqs, plain_memo), dtype)
 
 
 def test_slots_and_pages_used_again_start_clean(bobunex_dirs, plain_memo, tmp_path):

@@ -90,7 +90,9 @@ _SIGNATURES: dict[str, list] = {
     "tm_qk_norm_rope_write": [_I, _P, _LL, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P],
     "tm_sink_attention": [_I, _P, _P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P],
     "tm_sink_attention_mma_bf16": [_P, _P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P],
-    "tm_matrix_memory": [_P, _LL, _I, _I, _I, _I, _I, _P, _P, _F, _F, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I, _P],
+    "tm_matrix_memory": [_P, _LL, _I, _I, _I, _I, _I, _P, _P, _F, _F, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _LL,
+                         _I, _P],
+    "tm_matrix_memory_pass_states": [_P, _LL, _LL, _P, _P, _I, _I, _I, _I, _I, _P, _LL, _P],
     "tm_argmax": [_P, _I, _I, _LL, _P, _P, _P, _P],
     "tm_sample": [_P, _I, _I, _LL, _P, _P, _P, _P, _P, _P, _I, _P, _P],
 }
@@ -102,7 +104,7 @@ _HYBRID = {"tm_add_norm_pair", "tm_token_shift", "tm_gated_group_norm", "tm_late
            "tm_latent_attention_mma_bf16", "tm_conv_silu_state", "tm_ssm_scan", "tm_ssm_pass_states", "tm_relu2",
            "tm_moe_topk", "tm_glu_routed", "tm_gemm_f32_nt_batched"}
 _GATED = {"tm_gated_add_rmsnorm", "tm_canon_conv", "tm_glu", "tm_norm_pair_mean", "tm_head_norm_gate",
-          "tm_qk_norm_rope_write", "tm_sink_attention", "tm_sink_attention_mma_bf16", "tm_matrix_memory"}
+          "tm_qk_norm_rope_write", "tm_sink_attention", "tm_sink_attention_mma_bf16", "tm_matrix_memory", "tm_matrix_memory_pass_states"}
 _BOTH = {"tm_gemm_f32_nt"}            # in every library
 
 

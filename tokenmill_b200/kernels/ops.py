@@ -1191,17 +1191,39 @@ def matrix_memory_state_floats(heads: int, dim: int, vdim: int) -> int:
 def matrix_memory(proj: torch.Tensor, *, q_col: int, k_col: int, v_col: int, i_col: int, f_col: int,
                   i_bias: torch.Tensor | None, f_bias: torch.Tensor | None, cap: float, q_scale: float,
                   state: torch.Tensor, state_off: int, cu_q: torch.Tensor, state_slots: torch.Tensor, y: torch.Tensor,
-                  n_seqs: int, heads: int, dim: int, vdim: int) -> torch.Tensor:
+                  n_seqs: int, heads: int, dim: int, vdim: int, slice_len: int = 0,
+                  slices: torch.Tensor | None = None) -> torch.Tensor:
     """The recurrence over this step's tokens. proj [T, P] float32 (rows may be strided) holds q, k (heads x dim), v
     (heads x vdim) and the raw gates (heads each) at the named columns; y [T, heads * vdim] float32; a request's memory
-    lives at ``state_off`` inside its slot of ``state`` [slots, n] float32."""
+    lives at ``state_off`` inside its slot of ``state`` [slots, n] float32. ``slice_len`` > 0: three passes over time
+    slices of that many tokens (for long prompt portions), through ``slices``, float32 scratch for
+    ``matrix_memory_slice_records(T, n_seqs, slice_len)`` records of ``matrix_memory_state_floats`` floats."""
     T = proj.shape[0]
+    floats = matrix_memory_state_floats(heads, dim, vdim)
     if proj.dtype != torch.float32 or proj.stride(1) != 1 or y.shape != (T, heads * vdim) or dim > 1024 or \
-            state.shape[1] < state_off + matrix_memory_state_floats(heads, dim, vdim) or state.stride(1) != 1:
+            state.shape[1] < state_off + floats or state.stride(1) != 1:
         raise lib.KernelError("matrix_memory: shapes do not fit")
-    lib.call("tm_matrix_memory", proj.data_ptr(), proj.stride(0), q_col, k_col, v_col, i_col, f_col,
-             _opt(i_bias, "i_bias", torch.float32), _opt(f_bias, "f_bias", torch.float32), float(cap), float(q_scale),
-             _req(state, "state", torch.float32), state.stride(0), int(state_off), _req(cu_q, "cu_q", torch.int32),
-             _req(state_slots, "state_slots", torch.int32), _req(y, "y", torch.float32), int(n_seqs), heads, dim, vdim,
-             _stream())
+    records = matrix_memory_slice_records(T, n_seqs, slice_len) if slice_len > 0 else 0
+    if slice_len > 0 and (slices is None or slices.numel() < records * floats):
+        raise lib.KernelError("matrix_memory: scratch for the time slices is missing or too small")
+
+    def walk(mode):
+        lib.call("tm_matrix_memory", proj.data_ptr(), proj.stride(0), q_col, k_col, v_col, i_col, f_col,
+                 _opt(i_bias, "i_bias", torch.float32), _opt(f_bias, "f_bias", torch.float32), float(cap), float(q_scale),
+                 _req(state, "state", torch.float32), state.stride(0), int(state_off), _req(cu_q, "cu_q", torch.int32),
+                 _req(state_slots, "state_slots", torch.int32), _req(y, "y", torch.float32), int(n_seqs), heads, dim, vdim,
+                 mode, int(slice_len), _opt(slices, "slices", torch.float32), floats, records, _stream())
+
+    if slice_len <= 0:
+        walk(0)
+        return y
+    walk(1)
+    lib.call("tm_matrix_memory_pass_states", state.data_ptr(), state.stride(0), int(state_off), cu_q.data_ptr(),
+             state_slots.data_ptr(), int(n_seqs), heads, dim, vdim, int(slice_len), slices.data_ptr(), floats, _stream())
+    walk(2)
     return y
+
+
+def matrix_memory_slice_records(n_tokens: int, n_seqs: int, slice_len: int) -> int:
+    """Slice records a step needs: request s owns records cu_q[s] // slice_len + s onwards."""
+    return n_tokens // slice_len + n_seqs

@@ -23,6 +23,10 @@ from .base import LayerCache, StepInputs
 from .spec import StateNeed, WeightSpec
 
 
+SLICED_FROM = 256       # a step whose longest portion has this many tokens runs the recurrence over time slices
+SLICE_LEN = 128
+
+
 class MatrixMemoryMixer:
     def __init__(self, *, hidden_size: int, num_heads: int, head_dim: int, value_dim: int, gate_cap: float = 0.0,
                  eps: float = 1e-6, names: dict[str, str] | None = None, dtype: torch.dtype, device: torch.device):
@@ -82,10 +86,16 @@ class MatrixMemoryMixer:
         ``state_off`` floats into its slot."""
         T, dev, c = proj.shape[0], proj.device, self.col
         y = torch.empty((T, self.inner), dtype=torch.float32, device=dev)
+        # Long portions: three passes over time slices instead of one walk over the whole portion (kernels/ops.py).
+        sliced = {}
+        if step.max_q_len >= SLICED_FROM and step.workspace is not None:
+            records = ops.matrix_memory_slice_records(T, step.n_seqs, SLICE_LEN)
+            sliced = dict(slice_len=SLICE_LEN,
+                          slices=step.workspace.get("matrix_memory_slices", records * self.state_floats, torch.float32))
         ops.matrix_memory(proj, q_col=c["q"], k_col=c["k"], v_col=c["v"], i_col=c["i"], f_col=c["f"], i_bias=self.b_i,
                           f_bias=self.b_f, cap=self.cap, q_scale=self.d ** -0.5, state=cache.state, state_off=state_off,
                           cu_q=step.cu_q, state_slots=step.state_slots, y=y, n_seqs=step.n_seqs, heads=self.nh, dim=self.d,
-                          vdim=self.dv)
+                          vdim=self.dv, **sliced)
         gated = torch.empty((T, self.inner), dtype=self.dtype, device=dev)
         ops.head_norm_gate(y, proj[:, c["g"]:c["g"] + self.inner], self.g, self.eps, self.nh, gated)
         return ops.linear(gated, self.w_o)
