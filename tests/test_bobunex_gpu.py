@@ -394,10 +394,11 @@ def test_matrix_memory_kernel_under_cuts(heads, d, dv):
     for na, nb in ((1, 17), (20, 1), (2, 1), (17, 21)):
         rows = torch.cat([seqs[0][fed[0]:fed[0] + na], seqs[1][fed[1]:fed[1] + nb]]).to(DEV)
         cu, _, slots = _step_arrays([na, nb], [1, 3])
-        y = torch.empty(na + nb, heads * dv, device=DEV)
+        y, den = torch.empty(na + nb, heads * dv, device=DEV), torch.empty(na + nb, heads, device=DEV)
         ops.matrix_memory(rows[:, 5:], q_col=col["q"], k_col=col["k"], v_col=col["v"], i_col=col["i"], f_col=col["f"],
                           i_bias=bi.to(DEV), f_bias=bf.to(DEV), cap=cap, q_scale=d ** -0.5, state=state, state_off=8, cu_q=cu,
-                          state_slots=slots, y=y, n_seqs=2, heads=heads, dim=d, vdim=dv)
+                          state_slots=slots, y=y, den=den, n_seqs=2, heads=heads, dim=d, vdim=dv)
+        y = (y.view(-1, heads, dv) / den[:, :, None]).view(-1, heads * dv)
         ref = torch.cat([want[0][fed[0]:fed[0] + na], want[1][fed[1]:fed[1] + nb]])
         assert (y.cpu().double() - ref).abs().max() < 2e-5 * max(1.0, float(ref.abs().max()))
         fed = [fed[0] + na, fed[1] + nb]
@@ -422,15 +423,16 @@ def test_matrix_memory_over_time_slices(heads, d, dv, slice_len):
     for sliced in (False, True):
         state = torch.zeros(5, floats, device=DEV)
         cu, _, slots = _step_arrays([3, 3, 3], [4, 0, 2])
-        ops.matrix_memory(warm, state=state, cu_q=cu, state_slots=slots, y=torch.empty(9, heads * dv, device=DEV), **kw)
+        ops.matrix_memory(warm, state=state, cu_q=cu, state_slots=slots, y=torch.empty(9, heads * dv, device=DEV),
+                          den=torch.empty(9, heads, device=DEV), **kw)
         cu, _, slots = _step_arrays([61, 1, 16], [4, 0, 2])
-        y = torch.empty(78, heads * dv, device=DEV)
+        y, den = torch.empty(78, heads * dv, device=DEV), torch.empty(78, heads, device=DEV)
         extra = {}
         if sliced:
             n = ops.matrix_memory_slice_records(78, 3, slice_len)
             extra = dict(slice_len=slice_len, slices=torch.full((n * floats,), float("nan"), device=DEV))
-        ops.matrix_memory(rows, state=state, cu_q=cu, state_slots=slots, y=y, **kw, **extra)
-        results.append((y.cpu(), state.cpu()))
+        ops.matrix_memory(rows, state=state, cu_q=cu, state_slots=slots, y=y, den=den, **kw, **extra)
+        results.append(((y.view(-1, heads, dv) / den[:, :, None]).view(-1, heads * dv).cpu(), state.cpu()))
     (y0, s0), (y1, s1) = results
     assert (y0 - y1).abs().max() < 2e-5 * max(1.0, float(y0.abs().max()))
     assert (s0 - s1).abs().max() < 2e-5 * max(1.0, float(s0.abs().max()))

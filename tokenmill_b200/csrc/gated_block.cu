@@ -18,8 +18,8 @@
 //
 // tm_norm_pair_mean: out = (rmsnorm(a) wa + rmsnorm(b) wb) / 2, each row of a and b by its own root mean square.
 //
-// tm_head_norm_gate: y [T, heads, dv] float32 -> each head divided by its root mean square, times weight, times
-// sigmoid(gate pre-activation read from a 32-bit product).
+// tm_head_norm_gate: y [T, heads, dv] float32 (first divided by den[T, heads], where given) -> each head divided by its
+// root mean square, times weight, times sigmoid(gate pre-activation read from a 32-bit product).
 #include "common.cuh"
 
 namespace tmk {
@@ -64,11 +64,15 @@ __global__ void __launch_bounds__(256) gated_add_rmsnorm_kernel(
 
 constexpr int kMaxTaps = 16;
 
-template <typename T>
+// TAPS > 0: the number of taps is known when compiling (every loop unrolls, the carried inputs sit in registers);
+// TAPS == 0: any number up to kMaxTaps. `vec`: C is a multiple of 4 and a thread takes four channels per access.
+template <typename T, int TAPS>
 __global__ void __launch_bounds__(256) canon_conv_kernel(
     const T* __restrict__ h, const float* __restrict__ w, float* __restrict__ state, long long state_stride,
     const int* __restrict__ cu_q, const int* __restrict__ seq_of_token, const int* __restrict__ state_slots,
-    T* __restrict__ out, int C, int taps) {
+    T* __restrict__ out, int C, int taps_rt, int vec) {
+  constexpr int MAXT = TAPS > 0 ? TAPS : kMaxTaps;
+  const int taps = TAPS > 0 ? TAPS : taps_rt;
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -77,6 +81,23 @@ __global__ void __launch_bounds__(256) canon_conv_kernel(
   const int local = t - first;
   const int carry = taps - 1;
   if (local >= carry) {                     // every tap lies inside the step
+    if (vec) {
+      for (int c = threadIdx.x * 4; c < C; c += blockDim.x * 4) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f}, v[4];
+#pragma unroll
+        for (int j = 0; j < MAXT; ++j) {
+          if (j < taps) {
+            load4(h + (size_t)(t - carry + j) * C + c, v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[e] = fmaf(w[(size_t)(c + e) * taps + j], v[e], acc[e]);
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[e] += v[e];         // the last tap's input is h[t]
+        store4(out + (size_t)t * C + c, acc);
+      }
+      return;
+    }
     for (int c = threadIdx.x; c < C; c += blockDim.x) {
       float acc = 0.f;
       for (int j = 0; j < taps; ++j) acc = fmaf(w[(size_t)c * taps + j], to_float(h[(size_t)(t - carry + j) * C + c]), acc);
@@ -89,64 +110,133 @@ __global__ void __launch_bounds__(256) canon_conv_kernel(
   const int n = end - first;
   const int head = min(n, carry);
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    float old[kMaxTaps], wt[kMaxTaps];
-    for (int j = 0; j < carry; ++j) old[j] = slot[(size_t)j * C + c];
-    for (int j = 0; j < taps; ++j) wt[j] = w[(size_t)c * taps + j];
-    for (int r = 0; r < head; ++r) {        // row first + r reads positions r - carry .. r of the step
-      float acc = 0.f;
-      for (int j = 0; j < taps; ++j) {
-        const int p = r - carry + j;        // p < 0: slot entry carry + p
-        const float v = p < 0 ? old[carry + p] : to_float(h[(size_t)(first + p) * C + c]);
-        acc = fmaf(wt[j], v, acc);
-      }
-      out[(size_t)(first + r) * C + c] = from_float<T>(to_float(h[(size_t)(first + r) * C + c]) + acc);
+    float old[MAXT], wt[MAXT], cur[MAXT];   // carried inputs, weights, the step's first inputs
+#pragma unroll
+    for (int j = 0; j < MAXT; ++j) {
+      old[j] = j < carry ? slot[(size_t)j * C + c] : 0.f;
+      wt[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
+      cur[j] = j < head ? to_float(h[(size_t)(first + j) * C + c]) : 0.f;
     }
-    for (int j = 0; j < carry; ++j) {       // the last `carry` inputs of (old inputs ++ this step's)
-      const int p = n - carry + j;
-      slot[(size_t)j * C + c] = p < 0 ? old[carry + p] : to_float(h[(size_t)(first + p) * C + c]);
+#pragma unroll
+    for (int r = 0; r < MAXT; ++r) {        // row first + r reads positions r - carry .. r of the step
+      if (r < head) {
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < MAXT; ++j) {
+          if (j < taps) {
+            const int p = r - carry + j;    // p < 0: slot entry carry + p
+            float v = 0.f;
+#pragma unroll
+            for (int i = 0; i < MAXT; ++i) {
+              if (p < 0 && i == carry + p) v = old[i];
+              if (p >= 0 && i == p) v = cur[i];
+            }
+            acc = fmaf(wt[j], v, acc);
+          }
+        }
+        out[(size_t)(first + r) * C + c] = from_float<T>(cur[r] + acc);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < MAXT; ++j) {        // the last `carry` inputs of (old inputs ++ this step's)
+      if (j < carry) {
+        const int p = n - carry + j;
+        float v = 0.f;
+        if (p >= head) {
+          v = to_float(h[(size_t)(first + p) * C + c]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < MAXT; ++i) {
+            if (p < 0 && i == carry + p) v = old[i];
+            if (p >= 0 && i == p) v = cur[i];
+          }
+        }
+        slot[(size_t)j * C + c] = v;
+      }
     }
   }
 }
 
+// tanh as 1 - 2 / (exp(2x) + 1): absolute error of the order of 1e-7 in 32-bit
+__device__ __forceinline__ float fast_tanh(float x) { return 1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f); }
+
 __device__ __forceinline__ float gelu_tanh(float z) {
-  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return 0.5f * z * (1.0f + fast_tanh(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <int ACT> __device__ __forceinline__ float glu_act(float g) {
+  return ACT == 0 ? g / (1.0f + expf(-g)) : gelu_tanh(g);
 }
 
 template <typename T, int ACT>
-__global__ void __launch_bounds__(256) glu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I) {
+__global__ void __launch_bounds__(256) glu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int vec) {
   pdl_launch_dependents();
   pdl_wait();
   const long long t = blockIdx.x;
+  if (vec) {                                // I a multiple of 4: four elements per access
+    const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+    if (i >= I) return;
+    float g[4], u[4];
+    load4(gu + t * 2 * I + i, g);
+    load4(gu + t * 2 * I + I + i, u);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) g[e] = glu_act<ACT>(g[e]) * u[e];
+    store4(out + t * I + i, g);
+    return;
+  }
   const int i = blockIdx.y * blockDim.x + threadIdx.x;
   if (i >= I) return;
-  const float g = to_float(gu[t * 2 * I + i]), u = to_float(gu[t * 2 * I + I + i]);
-  const float a = ACT == 0 ? g / (1.0f + expf(-g)) : gelu_tanh(g);
-  out[t * I + i] = from_float<T>(a * u);
+  out[t * I + i] = from_float<T>(glu_act<ACT>(to_float(gu[t * 2 * I + i])) * to_float(gu[t * 2 * I + I + i]));
 }
 
 template <typename T>
 __global__ void __launch_bounds__(256) norm_pair_mean_kernel(const T* __restrict__ a, const T* __restrict__ b,
                                                              const float* __restrict__ wa, const float* __restrict__ wb,
-                                                             float eps, T* __restrict__ out, int H) {
+                                                             float eps, T* __restrict__ out, int H, int vec) {
   __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
   const size_t row = (size_t)blockIdx.x * H;
   float sa = 0.f, sb = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    const float x = to_float(a[row + i]), y = to_float(b[row + i]);
-    sa += x * x;
-    sb += y * y;
+  if (vec) {                                // H a multiple of 4: four elements per access
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      float x[4], y[4];
+      load4(a + row + i, x);
+      load4(b + row + i, y);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        sa += x[e] * x[e];
+        sb += y[e] * y[e];
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      const float x = to_float(a[row + i]), y = to_float(b[row + i]);
+      sa += x * x;
+      sb += y * y;
+    }
   }
   const float ra = 1.0f / sqrtf(block_sum(sa, red) / (float)H + eps);
   const float rb = 1.0f / sqrtf(block_sum(sb, red) / (float)H + eps);
+  if (vec) {
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      float x[4], y[4];
+      load4(a + row + i, x);
+      load4(b + row + i, y);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) x[e] = 0.5f * (x[e] * ra * wa[i + e] + y[e] * rb * wb[i + e]);
+      store4(out + row + i, x);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < H; i += blockDim.x)
     out[row + i] = from_float<T>(0.5f * (to_float(a[row + i]) * ra * wa[i] + to_float(b[row + i]) * rb * wb[i]));
 }
 
 // One warp per (row, head).
 template <typename T>
-__global__ void __launch_bounds__(128) head_norm_gate_kernel(const float* __restrict__ y, const float* __restrict__ gate,
+__global__ void __launch_bounds__(128) head_norm_gate_kernel(const float* __restrict__ y, const float* __restrict__ den,
+                                                             const float* __restrict__ gate,
                                                              long long gate_stride, const float* __restrict__ w, float eps,
                                                              T* __restrict__ out, int heads, int dv, long long n_pairs) {
   pdl_launch_dependents();
@@ -157,13 +247,17 @@ __global__ void __launch_bounds__(128) head_norm_gate_kernel(const float* __rest
   const long long t = pair / heads;
   const int hd = (int)(pair - t * heads);
   const float* src = y + (size_t)pair * dv;
+  const float dn = den ? den[pair] : 1.f;
   float ss = 0.f;
-  for (int i = lane; i < dv; i += 32) ss += src[i] * src[i];
+  for (int i = lane; i < dv; i += 32) {
+    const float o = src[i] / dn;
+    ss += o * o;
+  }
   const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
   for (int i = lane; i < dv; i += 32) {
     const int c = hd * dv + i;
     const float z = gate[(size_t)t * gate_stride + c];
-    out[(size_t)pair * dv + i] = from_float<T>(src[i] * rstd * w[c] / (1.0f + expf(-z)));
+    out[(size_t)pair * dv + i] = from_float<T>(src[i] / dn * rstd * w[c] / (1.0f + expf(-z)));
   }
 }
 
@@ -203,18 +297,29 @@ extern "C" int tm_canon_conv(int dtype, const void* h, const float* w, float* st
                              int taps, cudaStream_t stream) {
   if (T_rows <= 0) return 0;
   if (taps < 1 || taps > kMaxTaps) return TM_ERR_UNSUPPORTED_SHAPE;
-  TM_BY_DTYPE(dtype, return launch_pdl(canon_conv_kernel<T>, dim3(T_rows), dim3(256), 0, stream, (const T*)h, w, state,
-                                       state_stride, cu_q, seq_of_token, state_slots, (T*)out, C, taps))
+  const int vec = C % 4 == 0;
+#define TM_CANON(TT)                                                                                                   \
+  return launch_pdl(canon_conv_kernel<T, TT>, dim3(T_rows), dim3(256), 0, stream, (const T*)h, w, state, state_stride, cu_q, \
+                    seq_of_token, state_slots, (T*)out, C, taps, vec);
+  TM_BY_DTYPE(dtype, {
+    switch (taps) {
+      case 1: TM_CANON(1) case 2: TM_CANON(2) case 3: TM_CANON(3) case 4: TM_CANON(4) case 5: TM_CANON(5) case 6: TM_CANON(6)
+      case 7: TM_CANON(7) case 8: TM_CANON(8)
+      default: TM_CANON(0)
+    }
+  })
+#undef TM_CANON
 }
 
 // gu [T, 2 I] (gate columns first) -> out [T, I]; act 0: silu, 1: gelu (tanh form).
 extern "C" int tm_glu(int dtype, int act, const void* gu, void* out, int T_rows, int I, cudaStream_t stream) {
   if (T_rows <= 0) return 0;
   if (act != 0 && act != 1) return TM_ERR_UNSUPPORTED_SHAPE;
-  const dim3 grid(T_rows, (I + 255) / 256);
+  const int vec = I % 4 == 0;
+  const dim3 grid(T_rows, vec ? (I / 4 + 255) / 256 : (I + 255) / 256);
   TM_BY_DTYPE(dtype, {
-    if (act == 0) return launch_pdl(glu_kernel<T, 0>, grid, dim3(256), 0, stream, (const T*)gu, (T*)out, I);
-    return launch_pdl(glu_kernel<T, 1>, grid, dim3(256), 0, stream, (const T*)gu, (T*)out, I);
+    if (act == 0) return launch_pdl(glu_kernel<T, 0>, grid, dim3(256), 0, stream, (const T*)gu, (T*)out, I, vec);
+    return launch_pdl(glu_kernel<T, 1>, grid, dim3(256), 0, stream, (const T*)gu, (T*)out, I, vec);
   })
 }
 
@@ -222,14 +327,15 @@ extern "C" int tm_norm_pair_mean(int dtype, const void* a, const void* b, const 
                                  void* out, int T_rows, int H, cudaStream_t stream) {
   if (T_rows <= 0) return 0;
   TM_BY_DTYPE(dtype, return launch_pdl(norm_pair_mean_kernel<T>, dim3(T_rows), dim3(256), 0, stream, (const T*)a,
-                                       (const T*)b, wa, wb, eps, (T*)out, H))
+                                       (const T*)b, wa, wb, eps, (T*)out, H, (int)(H % 4 == 0)))
 }
 
-// y [T, heads * dv] float; gate: float pre-activations, element (t, c) at gate + t * gate_stride + c; w [heads * dv].
-extern "C" int tm_head_norm_gate(int dtype, const float* y, const float* gate, long long gate_stride, const float* w,
+// y [T, heads * dv] float; den [T, heads] float or null; gate: float pre-activations, element (t, c) at
+// gate + t * gate_stride + c; w [heads * dv].
+extern "C" int tm_head_norm_gate(int dtype, const float* y, const float* den, const float* gate, long long gate_stride, const float* w,
                                  float eps, void* out, int T_rows, int heads, int dv, cudaStream_t stream) {
   if (T_rows <= 0) return 0;
   const long long pairs = (long long)T_rows * heads;
   TM_BY_DTYPE(dtype, return launch_pdl(head_norm_gate_kernel<T>, dim3((unsigned)((pairs + 3) / 4)), dim3(128), 0, stream, y,
-                                       gate, gate_stride, w, eps, (T*)out, heads, dv, pairs))
+                                       den, gate, gate_stride, w, eps, (T*)out, heads, dv, pairs))
 }

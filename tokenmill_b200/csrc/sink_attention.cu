@@ -28,6 +28,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope_write_kernel(
     const float* __restrict__ wk, float eps, const int* __restrict__ positions, const float* __restrict__ cos_t,
     const float* __restrict__ sin_t, int n_positions, const int* __restrict__ slot_map, T* __restrict__ q_out,
     T* __restrict__ cache, float* __restrict__ gate_out, int* __restrict__ error) {
+  extern __shared__ __align__(16) float staged[];    // the token's q and k columns: read once, used three times
   __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
@@ -43,24 +44,24 @@ __global__ void __launch_bounds__(256) qk_norm_rope_write_kernel(
   const float* ct = cos_t + (size_t)pos * half;
   const float* st = sin_t + (size_t)pos * half;
 
+  float sq = 0.f, sk = 0.f;
+  for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
+    const float v = row[i];
+    staged[i] = v;
+    if (i < nq) sq += v * v;
+    else sk += v * v;
+  }
   float rq = 1.f, rk = 1.f;
-  if (wq) {
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < nq; i += blockDim.x) ss += row[i] * row[i];
-    rq = 1.0f / sqrtf(block_sum(ss, red) / (float)nq + eps);
-  }
-  if (wk) {
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < nk; i += blockDim.x) ss += row[nq + i] * row[nq + i];
-    rk = 1.0f / sqrtf(block_sum(ss, red) / (float)nk + eps);
-  }
+  if (wq) rq = 1.0f / sqrtf(block_sum(sq, red) / (float)nq + eps);
+  if (wk) rk = 1.0f / sqrtf(block_sum(sk, red) / (float)nk + eps);
+  if (!wq && !wk) __syncthreads();
   const int slot = slot_map ? slot_map[t] : -1;
   T* crow = slot >= 0 ? cache + (size_t)slot * (nk + nv) : nullptr;
   for (int idx = threadIdx.x; idx < nq + nk; idx += blockDim.x) {
     const bool is_q = idx < nq;
     if (!is_q && !crow) continue;
     const int i = is_q ? idx : idx - nq;
-    const float* src = is_q ? row : row + nq;
+    const float* src = is_q ? staged : staged + nq;
     const float* w = is_q ? wq : wk;
     const float r = is_q ? rq : rk;
     const int e = i % d;
@@ -261,12 +262,20 @@ extern "C" int tm_qk_norm_rope_write(int dtype, const float* proj, long long ld,
                                      float* gate_out, int T_rows, int* error, cudaStream_t stream) {
   if (T_rows <= 0) return 0;
   if (rot_dims % 2 || rot_dims > d || rot_dims < 0 || H <= 0 || G <= 0) return TM_ERR_UNSUPPORTED_SHAPE;
+  const size_t smem = (size_t)(H + G) * d * sizeof(float);
+  if (smem > 200 * 1024) return TM_ERR_UNSUPPORTED_SHAPE;
+  if (smem > 40 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(tmk::qk_norm_rope_write_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(tmk::qk_norm_rope_write_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
   if (dtype == TM_DTYPE_F32)
-    return tmk::launch_pdl(tmk::qk_norm_rope_write_kernel<float>, dim3(T_rows), dim3(256), 0, stream, proj, ld, H, G, d, dv,
+    return tmk::launch_pdl(tmk::qk_norm_rope_write_kernel<float>, dim3(T_rows), dim3(256), smem, stream, proj, ld, H, G, d, dv,
                            rot_dims, wq, wk, eps, positions, cos_t, sin_t, n_positions, slot_map, (float*)q_out,
                            (float*)cache, gate_out, error);
   if (dtype == TM_DTYPE_BF16)
-    return tmk::launch_pdl(tmk::qk_norm_rope_write_kernel<__nv_bfloat16>, dim3(T_rows), dim3(256), 0, stream, proj, ld, H, G,
+    return tmk::launch_pdl(tmk::qk_norm_rope_write_kernel<__nv_bfloat16>, dim3(T_rows), dim3(256), smem, stream, proj, ld, H, G,
                            d, dv, rot_dims, wq, wk, eps, positions, cos_t, sin_t, n_positions, slot_map,
                            (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, gate_out, error);
   return TM_ERR_BAD_DTYPE;

@@ -1099,14 +1099,15 @@ def norm_pair_mean(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch
 
 
 def head_norm_gate(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, heads: int,
-                   out: torch.Tensor) -> torch.Tensor:
-    """y [T, heads * dv] float32: each head by its own root mean square, times weight, times sigmoid(gate); gate
-    [T, heads * dv] float32 pre-activations (rows may be strided)."""
+                   out: torch.Tensor, den: torch.Tensor | None = None) -> torch.Tensor:
+    """y [T, heads * dv] float32 (divided by den [T, heads] first, where given): each head by its own root mean square,
+    times weight, times sigmoid(gate); gate [T, heads * dv] float32 pre-activations (rows may be strided)."""
     T, inner = y.shape
     if inner % heads or gate.shape != y.shape or gate.stride(1) != 1 or gate.dtype != torch.float32 or \
-            weight.numel() != inner or out.shape != y.shape:
+            weight.numel() != inner or out.shape != y.shape or (den is not None and den.shape != (T, heads)):
         raise lib.KernelError("head_norm_gate: shapes do not fit")
-    lib.call("tm_head_norm_gate", _code(out.dtype), _req(y, "y", torch.float32), gate.data_ptr(), gate.stride(0),
+    lib.call("tm_head_norm_gate", _code(out.dtype), _req(y, "y", torch.float32), _opt(den, "den", torch.float32),
+             gate.data_ptr(), gate.stride(0),
              _req(weight, "weight", torch.float32), float(eps), _req(out, "out"), T, heads, inner // heads, _stream())
     return out
 
@@ -1173,35 +1174,37 @@ MEMORY_THREADS = 256
 
 
 def matrix_memory_geometry(dim: int, vdim: int) -> tuple[int, int, int]:
-    """(d_pad, value columns per block, column tiles) of the matrix-memory kernel for heads of dim x vdim: a column's
+    """(d_pad, columns per block, column tiles) of the matrix-memory kernel for heads of dim x vdim (+ 1 column): a column's
     state is spread over ``parts`` lanes of 8, 16 or 32 rows each (csrc/matrix_memory.cu)."""
     R = 8 if dim <= 256 else 16 if dim <= 512 else 32
     parts = 1
     while parts * R < dim:
         parts *= 2
     cols = MEMORY_THREADS // parts
-    return parts * R, cols, -(-vdim // cols)
+    return parts * R, cols, -(-(vdim + 1) // cols)
 
 
 def matrix_memory_state_floats(heads: int, dim: int, vdim: int) -> int:
+    """Floats of a request's memory: S with n as one more column, [heads][vdim + 1][d_pad], and four per block."""
     d_pad, _cols, tiles = matrix_memory_geometry(dim, vdim)
-    return heads * vdim * d_pad + heads * tiles * (d_pad + 4)
+    return heads * (vdim + 1) * d_pad + heads * tiles * 4
 
 
 def matrix_memory(proj: torch.Tensor, *, q_col: int, k_col: int, v_col: int, i_col: int, f_col: int,
                   i_bias: torch.Tensor | None, f_bias: torch.Tensor | None, cap: float, q_scale: float,
                   state: torch.Tensor, state_off: int, cu_q: torch.Tensor, state_slots: torch.Tensor, y: torch.Tensor,
-                  n_seqs: int, heads: int, dim: int, vdim: int, slice_len: int = 0,
+                  den: torch.Tensor, n_seqs: int, heads: int, dim: int, vdim: int, slice_len: int = 0,
                   slices: torch.Tensor | None = None) -> torch.Tensor:
     """The recurrence over this step's tokens. proj [T, P] float32 (rows may be strided) holds q, k (heads x dim), v
-    (heads x vdim) and the raw gates (heads each) at the named columns; y [T, heads * vdim] float32; a request's memory
+    (heads x vdim) and the raw gates (heads each) at the named columns; y [T, heads * vdim] float32 receives S^T q and
+    den [T, heads] float32 what each head's y is still to be divided by (``head_norm_gate`` does); a request's memory
     lives at ``state_off`` inside its slot of ``state`` [slots, n] float32. ``slice_len`` > 0: three passes over time
     slices of that many tokens (for long prompt portions), through ``slices``, float32 scratch for
     ``matrix_memory_slice_records(T, n_seqs, slice_len)`` records of ``matrix_memory_state_floats`` floats."""
     T = proj.shape[0]
     floats = matrix_memory_state_floats(heads, dim, vdim)
     if proj.dtype != torch.float32 or proj.stride(1) != 1 or y.shape != (T, heads * vdim) or dim > 1024 or \
-            state.shape[1] < state_off + floats or state.stride(1) != 1:
+            den.shape != (T, heads) or state.shape[1] < state_off + floats or state.stride(1) != 1:
         raise lib.KernelError("matrix_memory: shapes do not fit")
     records = matrix_memory_slice_records(T, n_seqs, slice_len) if slice_len > 0 else 0
     if slice_len > 0 and (slices is None or slices.numel() < records * floats):
@@ -1211,8 +1214,8 @@ def matrix_memory(proj: torch.Tensor, *, q_col: int, k_col: int, v_col: int, i_c
         lib.call("tm_matrix_memory", proj.data_ptr(), proj.stride(0), q_col, k_col, v_col, i_col, f_col,
                  _opt(i_bias, "i_bias", torch.float32), _opt(f_bias, "f_bias", torch.float32), float(cap), float(q_scale),
                  _req(state, "state", torch.float32), state.stride(0), int(state_off), _req(cu_q, "cu_q", torch.int32),
-                 _req(state_slots, "state_slots", torch.int32), _req(y, "y", torch.float32), int(n_seqs), heads, dim, vdim,
-                 mode, int(slice_len), _opt(slices, "slices", torch.float32), floats, records, _stream())
+                 _req(state_slots, "state_slots", torch.int32), _req(y, "y", torch.float32), _req(den, "den", torch.float32),
+                 int(n_seqs), heads, dim, vdim, mode, int(slice_len), _opt(slices, "slices", torch.float32), floats, records, _stream())
 
     if slice_len <= 0:
         walk(0)

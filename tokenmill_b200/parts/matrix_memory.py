@@ -86,6 +86,7 @@ class MatrixMemoryMixer:
         ``state_off`` floats into its slot."""
         T, dev, c = proj.shape[0], proj.device, self.col
         y = torch.empty((T, self.inner), dtype=torch.float32, device=dev)
+        den = torch.empty((T, self.nh), dtype=torch.float32, device=dev)
         # Long portions: three passes over time slices instead of one walk over the whole portion (kernels/ops.py).
         sliced = {}
         if step.max_q_len >= SLICED_FROM and step.workspace is not None:
@@ -94,10 +95,10 @@ class MatrixMemoryMixer:
                           slices=step.workspace.get("matrix_memory_slices", records * self.state_floats, torch.float32))
         ops.matrix_memory(proj, q_col=c["q"], k_col=c["k"], v_col=c["v"], i_col=c["i"], f_col=c["f"], i_bias=self.b_i,
                           f_bias=self.b_f, cap=self.cap, q_scale=self.d ** -0.5, state=cache.state, state_off=state_off,
-                          cu_q=step.cu_q, state_slots=step.state_slots, y=y, n_seqs=step.n_seqs, heads=self.nh, dim=self.d,
+                          cu_q=step.cu_q, state_slots=step.state_slots, y=y, den=den, n_seqs=step.n_seqs, heads=self.nh, dim=self.d,
                           vdim=self.dv, **sliced)
         gated = torch.empty((T, self.inner), dtype=self.dtype, device=dev)
-        ops.head_norm_gate(y, proj[:, c["g"]:c["g"] + self.inner], self.g, self.eps, self.nh, gated)
+        ops.head_norm_gate(y, proj[:, c["g"]:c["g"] + self.inner], self.g, self.eps, self.nh, gated, den=den)
         return ops.linear(gated, self.w_o)
 
 
