@@ -211,7 +211,7 @@ def test_rotary_frequencies_with_wavelength_scaling():
     assert (cos.double() - ang.cos()).abs().max() < 1e-7 and (sin.double() - ang.sin()).abs().max() < 1e-7
 
 
-def _attend(dtype, H, G, d, dv, rot_dims, window, keep_first, softcap, sink, q_lens, starts, page=8, sharpen=None, tc=False, hot=None):
+def _attend(dtype, H, G, d, dv, rot_dims, window, keep_first, softcap, sink, q_lens, starts, page=8, sharpen=None, tc=False, hot=None, splits=1):
     """Kernel pair (norm + rotation + cache write, attention) over a paged cache filled step by step, against the plain
     attention over whole sequences. Returns (engine output, plain output) for the LAST step's rows."""
     from tokenmill_b200.kernels import ops
@@ -272,7 +272,9 @@ def _attend(dtype, H, G, d, dv, rot_dims, window, keep_first, softcap, sink, q_l
             outs = ops.sink_attention(q, cache, bt, _t(cu), _t(befores), _t(tile_seq), _t(tile_row0), int(tile_seq.size), gate,
                                       torch.empty(T, H * dv, dtype=dtype, device=DEV), heads=H, kv_heads=G, dim=d, vdim=dv,
                                       scale=0.3, softcap=softcap, window=window, keep_first=keep_first, sink=sink,
-                                      tensor_cores=tc)
+                                      tensor_cores=tc, n_splits=splits,
+                                      part=torch.full((int(tile_seq.size) * G * splits * 64 * (dv + 2),), float("nan"), device=DEV)
+                                      if splits > 1 else None)
     ref = []
     freqs = pb.rotary_frequencies(rot_dims, 100.0, None) if rot_dims else None
     for s in range(n_seq):
@@ -338,6 +340,9 @@ def test_tensor_core_attention_kernel(case):
     assert (got - ref).abs().max() < 3e-2 * max(1.0, float(ref.abs().max()))
     slow, _ = _attend(torch.bfloat16, q_lens=q_lens, starts=starts, tc=False, **case)
     assert (got - slow).abs().max() < 3e-2 * max(1.0, float(ref.abs().max()))
+    for splits in (2, 3, 8):            # key blocks dealt out over several blocks and merged (more splits than blocks too)
+        cut, _ = _attend(torch.bfloat16, q_lens=q_lens, starts=starts, tc=True, splits=splits, **case)
+        assert (cut - ref).abs().max() < 3e-2 * max(1.0, float(ref.abs().max())), splits
 
 
 @pytest.mark.parametrize("tc", [False, True])
@@ -348,7 +353,7 @@ def test_attention_window_edges_with_hot_keys(tc):
     blocks (31, 32, 63, 64, 128), in a prompt and in decoded tokens."""
     case = dict(H=4, G=2, d=64, dv=32, rot_dims=8, softcap=30.0, sink=True)
     hot = [5, 6, 31, 32, 63, 64, 100, 128, 129, 140]
-    kw = dict(q_lens=[230, 1, 1, 1], starts=[0, 133, 134, 209], hot=hot, tc=tc, **case)
+    kw = dict(q_lens=[230, 1, 1, 1], starts=[0, 133, 134, 209], hot=hot, tc=tc, splits=3 if tc else 1, **case)
     got, ref = _attend(torch.bfloat16, window=70, keep_first=6, **kw)
     assert (got - ref).abs().max() < 3e-2 * float(ref.abs().max())
     for dw, dk in ((1, 0), (-1, 0), (0, 1), (0, -1)):

@@ -84,12 +84,21 @@ __global__ void __launch_bounds__(256) canon_conv_kernel(
     if (vec) {
       for (int c = threadIdx.x * 4; c < C; c += blockDim.x * 4) {
         float acc[4] = {0.f, 0.f, 0.f, 0.f}, v[4];
+        float wv[4 * MAXT];                 // the four channels' weights lie side by side: 16 bytes per access
+        if (TAPS > 0) {
+#pragma unroll
+          for (int i = 0; i < TAPS; ++i) {
+            const float4 x = *reinterpret_cast<const float4*>(w + (size_t)c * TAPS + 4 * i);
+            wv[4 * i] = x.x; wv[4 * i + 1] = x.y; wv[4 * i + 2] = x.z; wv[4 * i + 3] = x.w;
+          }
+        }
 #pragma unroll
         for (int j = 0; j < MAXT; ++j) {
           if (j < taps) {
             load4(h + (size_t)(t - carry + j) * C + c, v);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) acc[e] = fmaf(w[(size_t)(c + e) * taps + j], v[e], acc[e]);
+            for (int e = 0; e < 4; ++e)
+              acc[e] = fmaf(TAPS > 0 ? wv[e * MAXT + j] : w[(size_t)(c + e) * taps + j], v[e], acc[e]);
           }
         }
 #pragma unroll

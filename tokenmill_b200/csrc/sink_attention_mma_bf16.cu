@@ -10,8 +10,11 @@
 // window's first key on; what lies between is never read. Because the blocks are anchored, a row's sums run in the same
 // order however the request was cut into steps. A warp multiplies its rows with the whole block (ldmatrix +
 // mma.sync m16n8k16), keeps maximum, sum and output in registers, and adds P V with V read through ldmatrix.trans. The
-// window bounds a row's keys, so a tile is never cut into key chunks and nothing is merged. tanh is taken as
-// 1 - 2 / (exp(2x) + 1) in 32-bit (absolute error of the order of 1e-7); P is rounded to bfloat16 for the second product.
+// window bounds a row's keys, so a prompt's tile is never cut into key chunks. A step of few rows (decoding) deals a
+// tile's key blocks out over `n_splits` blocks of the grid (block z takes key blocks z, z + n_splits, ...; the sink
+// belongs to z = 0); each leaves unnormalised sums with its maximum and denominator, and tm_sink_attention_combine
+// merges them in the order of z. tanh is taken as 1 - 2 / (exp(2x) + 1) in 32-bit (absolute error of the order of
+// 1e-7); P is rounded to bfloat16 for the second product.
 #include "mma_util.cuh"
 
 namespace tmk {
@@ -31,7 +34,7 @@ __global__ void __launch_bounds__(kSmWarps * 32) sink_attention_mma_kernel(
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_before,
     const int* __restrict__ tile_seq, const int* __restrict__ tile_row0, const float* __restrict__ gate,
     __nv_bfloat16* __restrict__ out, int H, int G, int page_size, float scale, float softcap, int window, int keep_first,
-    int sink) {
+    int sink, int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
   constexpr int THREADS = kSmWarps * 32;
   constexpr int CHK = DK / 8, CHV = DV / 8;     // 16-byte chunks per key / value row
   constexpr int TPR = THREADS / kSmBN;          // threads that share one key row when loading (2)
@@ -57,7 +60,9 @@ __global__ void __launch_bounds__(kSmWarps * 32) sink_attention_mma_kernel(
   const int keep_end = min(keep, j_lo);                           // kept keys that lie below the window's first key
   const int n_keep = (keep_end + kSmBN - 1) / kSmBN;              // blocks 0 .. n_keep - 1 hold them
   const int kb_first = max(n_keep * kSmBN, (j_lo / kSmBN) * kSmBN);
-  const int n_blocks = n_keep + (j_hi >= kb_first ? (j_hi - kb_first) / kSmBN + 1 : 0);
+  const int all_blocks = n_keep + (j_hi >= kb_first ? (j_hi - kb_first) / kSmBN + 1 : 0);
+  const int split = blockIdx.z;
+  const int n_blocks = all_blocks > split ? (all_blocks - split + n_splits - 1) / n_splits : 0;   // this block's share
   const int* table = block_table + (size_t)s * bt_stride;
 
   uint32_t qa[KS][4];
@@ -93,12 +98,15 @@ __global__ void __launch_bounds__(kSmWarps * 32) sink_attention_mma_kernel(
 
   float m_run[2], l_run[2];
   float o[NT][4];
-  m_run[0] = m_run[1] = sink ? 0.f : -INFINITY;
-  l_run[0] = l_run[1] = sink ? 1.f : 0.f;
+  m_run[0] = m_run[1] = (sink && split == 0) ? 0.f : -INFINITY;
+  l_run[0] = l_run[1] = (sink && split == 0) ? 1.f : 0.f;
 #pragma unroll
   for (int t = 0; t < NT; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
 
-  auto block_start = [&](int b) { return b < n_keep ? b * kSmBN : kb_first + (b - n_keep) * kSmBN; };
+  auto block_start = [&](int i) {               // the i-th key block of this block's share
+    const int b = split + i * n_splits;
+    return b < n_keep ? b * kSmBN : kb_first + (b - n_keep) * kSmBN;
+  };
   auto load_block = [&](int stage, int kb) {
     const uint32_t k_dst = smem_base + stage * (K_BYTES + V_BYTES), v_dst = k_dst + K_BYTES;
     const int row = tid / TPR, part = tid - row * TPR;
@@ -243,6 +251,20 @@ __global__ void __launch_bounds__(kSmWarps * 32) sink_attention_mma_kernel(
   }
   cp_async_wait<0>();
 
+  if (n_splits > 1) {                           // one of several: sums, maximum (log2 units) and denominator
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      if (p_row[hh] < 0) continue;
+      const int r = warp * 16 + (lane >> 2) + hh * 8;
+      const size_t prow = (((size_t)blockIdx.x * G + kvh) * n_splits + split) * kSmBM + r;
+      float* dst = part_o + prow * DV;
+#pragma unroll
+      for (int t = 0; t < NT; ++t)
+        *reinterpret_cast<float2*>(dst + t * 8 + cpair) = make_float2(o[t][2 * hh], o[t][2 * hh + 1]);
+      if ((lane & 3) == 0) *reinterpret_cast<float2*>(part_ml + prow * 2) = make_float2(m_run[hh], l_run[hh]);
+    }
+    return;
+  }
 #pragma unroll
   for (int hh = 0; hh < 2; ++hh) {
     if (p_row[hh] < 0) continue;
@@ -255,11 +277,49 @@ __global__ void __launch_bounds__(kSmWarps * 32) sink_attention_mma_kernel(
   }
 }
 
+// Merges the partial results of a tile's key splits in the order of the splits; one block per (tile, key/value head),
+// a warp per row in turn.
+__global__ void __launch_bounds__(256) sink_attention_combine_kernel(
+    const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ cu_q,
+    const int* __restrict__ tile_seq, const int* __restrict__ tile_row0, const float* __restrict__ gate,
+    __nv_bfloat16* __restrict__ out, int H, int G, int dv, int n_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int s = tile_seq[blockIdx.x], row0 = tile_row0[blockIdx.x], kvh = blockIdx.y;
+  const int Gq = H / G;
+  const int q_start = cu_q[s], q_len = cu_q[s + 1] - q_start;
+  const int n_rows = min(kSmBM, q_len * Gq - row0);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const size_t base = ((size_t)blockIdx.x * G + kvh) * n_splits;
+  for (int r = warp; r < n_rows; r += 8) {
+    float M = -INFINITY;
+    for (int z = 0; z < n_splits; ++z) M = fmaxf(M, part_ml[((base + z) * kSmBM + r) * 2]);
+    float L = 0.f;
+    for (int z = 0; z < n_splits; ++z) {
+      const float* ml = part_ml + ((base + z) * kSmBM + r) * 2;
+      if (ml[0] != -INFINITY) L += ml[1] * exp2f(ml[0] - M);
+    }
+    const int row = row0 + r;
+    const size_t o_row = (size_t)(q_start + row / Gq) * H + kvh * Gq + row % Gq;
+    float f = L > 0.f ? 1.0f / L : 0.f;
+    if (gate) f *= gate[o_row];
+    for (int e = lane; e < dv; e += 32) {
+      float acc = 0.f;
+      for (int z = 0; z < n_splits; ++z) {
+        const float mz = part_ml[((base + z) * kSmBM + r) * 2];
+        if (mz != -INFINITY) acc += part_o[((base + z) * kSmBM + r) * dv + e] * exp2f(mz - M);
+      }
+      out[o_row * dv + e] = __float2bfloat16_rn(acc * f);
+    }
+  }
+}
+
 template <int DK, int DV>
 int launch_sink_attention_mma(const void* q, const void* cache, int row_width, int v_off, const int* block_table,
                               int bt_stride, const int* cu_q, const int* kv_before, const int* tile_seq,
                               const int* tile_row0, int n_tiles, const float* gate, void* out, int H, int G, int page_size,
-                              float scale, float softcap, int window, int keep_first, int sink, cudaStream_t stream) {
+                              float scale, float softcap, int window, int keep_first, int sink, int n_splits, float* part_o,
+                              float* part_ml, cudaStream_t stream) {
   constexpr int STAGES = (DK + DV) >= 256 ? 2 : 3;
   const int smem = STAGES * kSmBN * (DK + DV) * 2;
   auto kern = sink_attention_mma_kernel<DK, DV, STAGES>;
@@ -267,28 +327,36 @@ int launch_sink_attention_mma(const void* q, const void* cache, int row_width, i
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return launch_pdl(kern, dim3(n_tiles, G), dim3(kSmWarps * 32), (size_t)smem, stream, (const __nv_bfloat16*)q,
-                    (const __nv_bfloat16*)cache, row_width, v_off, block_table, bt_stride, cu_q, kv_before, tile_seq,
-                    tile_row0, gate, (__nv_bfloat16*)out, H, G, page_size, scale, softcap, window, keep_first, sink);
+  const int st = launch_pdl(kern, dim3(n_tiles, G, n_splits), dim3(kSmWarps * 32), (size_t)smem, stream,
+                            (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, row_width, v_off, block_table, bt_stride, cu_q,
+                            kv_before, tile_seq, tile_row0, gate, (__nv_bfloat16*)out, H, G, page_size, scale, softcap, window,
+                            keep_first, sink, n_splits, part_o, part_ml);
+  if (st != 0 || n_splits == 1) return st;
+  return launch_pdl(sink_attention_combine_kernel, dim3(n_tiles, G), dim3(256), 0, stream, (const float*)part_o,
+                    (const float*)part_ml, cu_q, tile_seq, tile_row0, gate, (__nv_bfloat16*)out, H, G, DV, n_splits);
 }
 
 }  // namespace tmk
 
 // q [T, H, d] bfloat16; cache [pages, page_size, row_width] bfloat16 with head g's key at g * d and its value at
 // v_off + g * dv (row_width and v_off multiples of 8); tiles of 64 (token, head in group) rows of one request; gate
-// [T, H] float or null; out [T, H, dv] bfloat16. d and dv each 32, 64 or 128; the scale positive.
+// [T, H] float or null; out [T, H, dv] bfloat16. d and dv each 32, 64 or 128; the scale positive. n_splits > 1: a
+// tile's key blocks are dealt out over that many blocks, through part_o [n_tiles * G * n_splits, 64, dv] and part_ml
+// [n_tiles * G * n_splits, 64, 2] float, and merged by a second launch.
 extern "C" int tm_sink_attention_mma_bf16(const void* q, const void* cache, int row_width, int v_off,
                                           const int* block_table, int bt_stride, const int* cu_q, const int* kv_before,
                                           const int* tile_seq, const int* tile_row0, int n_tiles, const float* gate,
                                           void* out, int H, int G, int d, int dv, int page_size, float scale, float softcap,
-                                          int window, int keep_first, int sink, cudaStream_t stream) {
+                                          int window, int keep_first, int sink, int n_splits, float* part_o, float* part_ml,
+                                          cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  if (n_splits < 1 || (n_splits > 1 && (!part_o || !part_ml))) return TM_ERR_SCRATCH_TOO_SMALL;
   if (G <= 0 || H % G || page_size <= 0 || (row_width & 7) || (v_off & 7) || !(scale > 0.f)) return TM_ERR_UNSUPPORTED_SHAPE;
 #define TM_SM_CASE(DKK, DVV)                                                                                          \
   if (d == DKK && dv == DVV)                                                                                          \
     return tmk::launch_sink_attention_mma<DKK, DVV>(q, cache, row_width, v_off, block_table, bt_stride, cu_q, kv_before, \
                                                     tile_seq, tile_row0, n_tiles, gate, out, H, G, page_size, scale, softcap, \
-                                                    window, keep_first, sink, stream);
+                                                    window, keep_first, sink, n_splits, part_o, part_ml, stream);
   TM_SM_CASE(32, 32) TM_SM_CASE(32, 64) TM_SM_CASE(32, 128) TM_SM_CASE(64, 32) TM_SM_CASE(64, 64) TM_SM_CASE(64, 128)
   TM_SM_CASE(128, 32) TM_SM_CASE(128, 64) TM_SM_CASE(128, 128)
 #undef TM_SM_CASE

@@ -89,7 +89,8 @@ _SIGNATURES: dict[str, list] = {
     "tm_head_norm_gate": [_I, _P, _P, _P, _LL, _P, _F, _P, _I, _I, _I, _P],
     "tm_qk_norm_rope_write": [_I, _P, _LL, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P],
     "tm_sink_attention": [_I, _P, _P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P],
-    "tm_sink_attention_mma_bf16": [_P, _P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P],
+    "tm_sink_attention_mma_bf16": [_P, _P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _I,
+                                   _P, _P, _P],
     "tm_matrix_memory": [_P, _LL, _I, _I, _I, _I, _I, _P, _P, _F, _F, _P, _LL, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P,
                          _LL, _I, _P],
     "tm_matrix_memory_pass_states": [_P, _LL, _LL, _P, _P, _I, _I, _I, _I, _I, _P, _LL, _P],

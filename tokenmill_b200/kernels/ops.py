@@ -1146,20 +1146,29 @@ def sink_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tens
                    kv_before: torch.Tensor, tile_seq: torch.Tensor, tile_row0: torch.Tensor, n_tiles: int,
                    gate: torch.Tensor | None, out: torch.Tensor, *, heads: int, kv_heads: int, dim: int, vdim: int,
                    scale: float, softcap: float, window: int, keep_first: int, sink: bool,
-                   tensor_cores: bool = False) -> torch.Tensor:
+                   tensor_cores: bool = False, n_splits: int = 1, part: torch.Tensor | None = None) -> torch.Tensor:
     """q [T, H d]; cache [pages, page_size, 1, G d + G dv]; tiles of 32 (``tensor_cores``: 64) (token, head in group)
-    rows of one request; gate [T, H] float32 or None; out [T, H dv]."""
+    rows of one request; gate [T, H] float32 or None; out [T, H dv]. ``n_splits`` > 1 (tensor cores only): a tile's
+    key blocks dealt out over that many blocks and merged, through ``part``, float32 scratch of
+    n_tiles * G * n_splits * 64 * (dv + 2) numbers."""
     T = q.shape[0]
     row = kv_heads * (dim + vdim)
     if cache.shape[-1] != row or q.shape != (T, heads * dim) or out.shape != (T, heads * vdim):
         raise lib.KernelError("sink_attention: shapes do not fit")
     if tensor_cores:
+        part_o = part_ml = None
+        if n_splits > 1:
+            rows64 = int(n_tiles) * kv_heads * int(n_splits) * SINK_TC_TILE_ROWS
+            if part is None or part.dtype != torch.float32 or part.numel() < rows64 * (vdim + 2):
+                raise lib.KernelError("sink_attention: scratch for the key splits is missing or too small")
+            part_o, part_ml = part.data_ptr(), part.data_ptr() + rows64 * vdim * 4
         lib.call("tm_sink_attention_mma_bf16", _req(q, "q", torch.bfloat16), _req(cache, "cache", torch.bfloat16), row,
                  kv_heads * dim, _req(block_table, "block_table", torch.int32), block_table.stride(0),
                  _req(cu_q, "cu_q", torch.int32), _req(kv_before, "kv_before", torch.int32),
                  _req(tile_seq, "tile_seq", torch.int32), _req(tile_row0, "tile_row0", torch.int32), int(n_tiles),
                  _opt(gate, "gate", torch.float32), _req(out, "out", torch.bfloat16), heads, kv_heads, dim, vdim,
-                 cache.shape[1], float(scale), float(softcap), int(window), int(keep_first), int(bool(sink)), _stream())
+                 cache.shape[1], float(scale), float(softcap), int(window), int(keep_first), int(bool(sink)),
+                 int(n_splits), part_o, part_ml, _stream())
         return out
     lib.call("tm_sink_attention", _code(q.dtype), _req(q, "q"), _req(cache, "cache", q.dtype), row, kv_heads * dim,
              _req(block_table, "block_table", torch.int32), block_table.stride(0), _req(cu_q, "cu_q", torch.int32),

@@ -30,6 +30,10 @@ from .base import LayerCache, StepInputs, StepMetadata, StepShape, part_limit_po
 from .spec import PagedKVNeed, PartSpec, StateNeed, WeightSpec
 
 
+SPLIT_BLOCKS = 296      # blocks the tensor-core kernel should have in flight before a tile's keys stop being dealt out
+MAX_SPLITS = 8
+
+
 class SinkWindowAttention:
     def __init__(self, *, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, scale: float,
                  position: PartSpec | None, rot_dims: int = 0, window: int | None = None, keep_first: int = 0,
@@ -119,7 +123,14 @@ class SinkWindowAttention:
         tile_seq = np.repeat(np.arange(len(per_seq), dtype=np.int32), per_seq)
         first = np.cumsum(per_seq) - per_seq
         tile_row0 = ((np.arange(tile_seq.size) - np.repeat(first, per_seq)) * rows).astype(np.int32)
-        return StepMetadata({"tile_seq": tile_seq, "tile_row0": tile_row0}, {"n_tiles": int(tile_seq.size)},
+        # Few row tiles (decoding): deal each tile's key blocks out over several blocks of the grid. (A captured graph
+        # serves every context: it takes the split for the longest.)
+        n_tiles, splits = int(tile_seq.size), 1
+        if self.tensor_cores and n_tiles:
+            longest = shape.max_kv_len if shape.for_graph else int((shape.starts.astype(np.int64) + shape.q_lens).max())
+            keys = min(longest, self.window + self.keep_first + rows) if self.window else longest
+            splits = max(1, min((keys // 64 + 1) // 2, SPLIT_BLOCKS // (n_tiles * self.nkv), MAX_SPLITS))
+        return StepMetadata({"tile_seq": tile_seq, "tile_row0": tile_row0}, {"n_tiles": n_tiles, "n_splits": splits},
                             constant_in_graph=True)
 
     # --- run --------------------------------------------------------------------------------------------------
@@ -139,10 +150,15 @@ class SinkWindowAttention:
                                cache=rows if cache.writes else None, gate_out=gate)
         meta = step.meta[self.metadata_key()]
         heads = torch.empty((T, self.nh * self.dv), dtype=self.dtype, device=dev)
+        splits, part = meta.host["n_splits"], None
+        if splits > 1:
+            part = step.workspace.get("sink_attention_part", meta.host["n_tiles"] * self.nkv * splits * self.tile_rows *
+                                      (self.dv + 2), torch.float32)
         ops.sink_attention(q, cache.k, step.block_tables[cache.group], step.cu_q, step.kv_before, meta.arrays["tile_seq"],
                            meta.arrays["tile_row0"], meta.host["n_tiles"], gate, heads, heads=self.nh, kv_heads=self.nkv,
                            dim=self.d, vdim=self.dv, scale=self.scale, softcap=self.softcap, window=self.window,
-                           keep_first=self.keep_first, sink=self.sink, tensor_cores=self.tensor_cores)
+                           keep_first=self.keep_first, sink=self.sink, tensor_cores=self.tensor_cores, n_splits=splits,
+                           part=part)
         return ops.linear(heads, self.w_o)
 
 
