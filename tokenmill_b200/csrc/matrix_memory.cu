@@ -14,8 +14,9 @@
 // which the column of n produces. The division is left to the kernel that norms the heads (it reads both anyway).
 //
 // One block per (tile of columns, head, request). A column's d state values are spread over `parts` neighbouring lanes,
-// R = 8, 16 or 32 rows each (parts = the power of two >= d / R), and the dot product with q is finished by shuffles among
-// those lanes. Every block keeps m for itself. Layout of a request's state, from `state_off` (in floats) inside its slot:
+// R = 8, 16 or 32 rows each (parts = the power of two >= d / R; lane p takes rows 4 p .. 4 p + 3 of every group of
+// 4 * parts rows, so that neighbouring lanes read neighbouring 16 bytes of k and q in shared memory), and the dot product
+// with q is finished by shuffles among those lanes. Every block keeps m for itself. Layout of a request's state, from `state_off` (in floats) inside its slot:
 //   [heads][dv + 1][d_pad]                          (d_pad = parts * R; rows >= d stay zero; column dv is n)
 //   then [heads][col_tiles][4]: m of each block; in a slice record also F and mu (below).
 // Tokens are staged through shared memory 16 at a time (q, k, the tile's v columns, the factors made from the gates).
@@ -110,7 +111,8 @@ __global__ void __launch_bounds__(kMemThreads) matrix_memory_kernel(
   const bool live = col <= dv;                  // column dv carries n
   float* slot = state + (size_t)state_slots[s] * state_stride + state_off;
   float* record = MODE == 0 ? slot : slices + (size_t)blockIdx.z * slice_floats;
-  float* S_g = record + ((size_t)head * (dv + 1) + (live ? col : 0)) * d_pad + part * R;
+  const int gs = 4 * parts;                     // rows between a lane's groups of four
+  float* S_g = record + ((size_t)head * (dv + 1) + (live ? col : 0)) * d_pad + part * 4;
   float* aux = record + (size_t)heads * (dv + 1) * d_pad + ((size_t)head * col_tiles + tile) * 4;
 
   float S[R];
@@ -120,7 +122,7 @@ __global__ void __launch_bounds__(kMemThreads) matrix_memory_kernel(
     if (MODE == 1 || !live) {
       S[r] = S[r + 1] = S[r + 2] = S[r + 3] = 0.f;
     } else {
-      const float4 a = *reinterpret_cast<const float4*>(S_g + r);
+      const float4 a = *reinterpret_cast<const float4*>(S_g + (r >> 2) * gs);
       S[r] = a.x; S[r + 1] = a.y; S[r + 2] = a.z; S[r + 3] = a.w;
     }
   }
@@ -215,18 +217,18 @@ __global__ void __launch_bounds__(kMemThreads) matrix_memory_kernel(
       const float4 f4 = *reinterpret_cast<const float4*>(fac + tt * 4);
       const float a = f4.x;
       const float bv = f4.y * vs[tt * cols + col_local];
-      const float* kr = ks + tt * d_pad + part * R;
-      const float* qr = qs + tt * d_pad + part * R;
+      const float* kr = ks + tt * d_pad + part * 4;
+      const float* qr = qs + tt * d_pad + part * 4;
       float num = 0.f;
 #pragma unroll
       for (int r = 0; r < R; r += 4) {
-        const float4 k4 = *reinterpret_cast<const float4*>(kr + r);
+        const float4 k4 = *reinterpret_cast<const float4*>(kr + (r >> 2) * gs);
         S[r] = fmaf(a, S[r], bv * k4.x);
         S[r + 1] = fmaf(a, S[r + 1], bv * k4.y);
         S[r + 2] = fmaf(a, S[r + 2], bv * k4.z);
         S[r + 3] = fmaf(a, S[r + 3], bv * k4.w);
         if (MODE != 1) {
-          const float4 q4 = *reinterpret_cast<const float4*>(qr + r);
+          const float4 q4 = *reinterpret_cast<const float4*>(qr + (r >> 2) * gs);
           num = fmaf(S[r], q4.x, num);
           num = fmaf(S[r + 1], q4.y, num);
           num = fmaf(S[r + 2], q4.z, num);
@@ -250,12 +252,13 @@ __global__ void __launch_bounds__(kMemThreads) matrix_memory_kernel(
 
   if (MODE == 2) {                              // only a request's last slice leaves a state: the slot's
     if (!last_slice) return;
-    S_g = slot + ((size_t)head * (dv + 1) + (live ? col : 0)) * d_pad + part * R;
+    S_g = slot + ((size_t)head * (dv + 1) + (live ? col : 0)) * d_pad + part * 4;
     aux = slot + (size_t)heads * (dv + 1) * d_pad + ((size_t)head * col_tiles + tile) * 4;
   }
   if (live) {
 #pragma unroll
-    for (int r = 0; r < R; r += 4) *reinterpret_cast<float4*>(S_g + r) = make_float4(S[r], S[r + 1], S[r + 2], S[r + 3]);
+    for (int r = 0; r < R; r += 4)
+      *reinterpret_cast<float4*>(S_g + (r >> 2) * gs) = make_float4(S[r], S[r + 1], S[r + 2], S[r + 3]);
   }
   if (tid == 0) {
     if (MODE == 1) {
