@@ -601,8 +601,10 @@ def test_first_tokens_and_single_token_requests(bobunex_dirs, plain_memo, tmp_pa
 
 # --- through the engine's own entry point -----------------------------------------------------------------------
 
-@pytest.mark.parametrize("graphs,chunked,dtype", [(False, False, "float32"), (True, True, "float32"), (False, True, "bfloat16")])
-def test_greedy_generation_through_the_engine(bobunex_dirs, graphs, chunked, dtype):
+@pytest.mark.parametrize("size,graphs,chunked,dtype", [
+    ("bobunex-tiny-a", False, False, "float32"), ("bobunex-tiny-a", True, True, "float32"),
+    ("bobunex-tiny-a", False, True, "bfloat16"), ("bobunex-tiny-d", True, True, "bfloat16")])
+def test_greedy_generation_through_the_engine(bobunex_dirs, size, graphs, chunked, dtype):
     """LLMEngine with its scheduler: admission (state slots, two page groups with kept first pages), chunked prompts
     beside decodes, decode graphs with padded rows, a pool so small that requests are evicted and recomputed. The
     logits behind every generated token equal the plain model's on the request's own history, and the token is their
@@ -611,16 +613,18 @@ def test_greedy_generation_through_the_engine(bobunex_dirs, graphs, chunked, dty
     from tokenmill_b200.engine import LLMEngine
     from tokenmill_b200.sampling import SamplingParams
 
-    folder = bobunex_dirs["bobunex-tiny-a"]
+    folder = bobunex_dirs[size]
     cfg, w = _read(folder)
     rng = random.Random(5)
-    prompts = [[rng.randrange(173) for _ in range(n)] for n in (9, 30, 17, 44, 5, 26, 12)]
-    per_token = (3 * (12 + 20) + 1 * (16 + 8)) * (4 if dtype == "float32" else 2)
+    prompts = [[rng.randrange(cfg["vocab"]) for _ in range(n)] for n in (9, 30, 17, 44, 5, 26, 12)]
+    lefts = [layer["mixer"]["left"] for layer in cfg["layers"]]
+    per_token = sum(a["kv_heads"] * (a["dim"] + a["vdim"]) for a in lefts) * (4 if dtype == "float32" else 2)
     eng = LLMEngine(EngineConfig(model=str(folder), dtype=dtype, block_size=8, max_model_len=128, max_num_seqs=4,
                                  kv_cache_mb=(16 * 8 + (8 if graphs else 0) + 1) * per_token / 2 ** 20, watermark=0.0,
                                  cuda_graphs=graphs, cuda_graph_max_batch=4, enable_chunked_prefill=chunked,
                                  max_num_batched_tokens=24 if chunked else 256))
-    assert eng.cache.state_slots.num_slots == 4 and len(eng.cache.num_pages) == 2 and eng.cache.keep_first == [3, 18]
+    assert eng.cache.state_slots.num_slots == 4 and len(eng.cache.num_pages) == 2
+    assert eng.cache.keep_first == [a["mask"]["keep_first"] for a in lefts]
     rows: dict[str, list] = {}
 
     def tap(where, logits):

@@ -58,7 +58,7 @@ class SinkWindowAttention:
         self.proj_width = self.q_size + self.k_size + self.v_size + (num_heads if self.head_gate else 0)
         # bfloat16 with key and value heads of 32, 64 or 128: tensor cores, 64 rows a tile; anything else (and the 32-bit
         # path): the shape-generic kernel on CUDA cores, 32 rows a tile
-        self.tensor_cores = ops.sink_attention_tc_ok(dtype, head_dim, value_dim)
+        self.tensor_cores = ops.sink_attention_tc_ok(dtype, head_dim, value_dim) and self.scale > 0
         self.tile_rows = ops.SINK_TC_TILE_ROWS if self.tensor_cores else ops.SINK_TILE_ROWS
         self.w_in = self.w_o = self.g_q = self.g_k = self.cos = self.sin = None
 
