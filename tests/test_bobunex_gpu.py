@@ -570,6 +570,27 @@ def test_time_sliced_memory_under_every_cut(bobunex_dirs, plain_memo, dtype, tmp
             _check(steps, outputs, reqs, _plain(folder, reqs, plain_memo), dtype)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_of_unlike_sizes_and_portions_beyond_the_slice_threshold(dtype, tmp_path):
+    """Three layers that share no size (three cache groups; one layer's heads take the tensor-core kernel in bfloat16,
+    the others do not; a memory of 96 rows), prompts of 300 and 270 tokens whole (the memory runs over time slices of
+    its real length, pages behind the windows go back while kept pages stay) and in mixed batches, then decoded."""
+    from tokenmill_b200.weights import write_random_model
+    from tokenmill_b200.weights.random_init import bobunex_attention as A, bobunex_config, bobunex_memory as M
+    cfg = bobunex_config(vocab=157, width=72, eps=1e-5, embedding_scale=0.7, taps=4, layers=[
+        (A(heads=10, kv_heads=5, dim=12, vdim=20, window=100, keep_first=33, scale=0.25, rot_dims=6, scaling=(8.0, 1.0, 4.0, 256)),
+         M(heads=3, dim=96, vdim=16, gate_cap=12.0), 88),
+        (A(heads=4, kv_heads=2, dim=64, vdim=64, window=40, keep_first=2, softcap=20.0, rot_dims=32), M(heads=2, dim=20, vdim=40), None),
+        (A(heads=3, kv_heads=3, dim=16, vdim=8, window=1000, keep_first=0, softcap=0.0, rot_dims=16), M(heads=6, dim=8, vdim=12, gate_cap=4.0), 40)])
+    folder = write_random_model(tmp_path / "m", cfg, seed=12)
+    _, w = _read(folder)
+    reqs = make_requests(157, [300, 270], seed=71)
+    plain = {r: _logits(cfg, w, t) for r, t in reqs.items()}
+    for mode in ("whole", "tail", "mixed"):
+        steps, max_tokens = _steps(mode, reqs)
+        _check(steps, run_trace(folder, dtype, steps, max_tokens, tmp_path / mode), reqs, plain, dtype)
+
+
 def test_slots_and_pages_used_again_start_clean(bobunex_dirs, plain_memo, tmp_path):
     """Nine requests through a pool for two live ones with two state slots: every slot and page is used several times,
     and a request that follows a long one on its slot gets the same logits as alone."""
